@@ -61,6 +61,9 @@ def read_config_json(folder) -> dict:
 
 
 def architecture_name(raw: dict) -> str:
+    """`architectures` (a list whose first entry is the model class) or `architecture` (its name as a string)."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) < 1 or not isinstance(archs[0], str):
         raise ConfigError("config.json: `architectures` must be a list with the model class name")

@@ -10,6 +10,8 @@
 // Reference: core/model.cpp:411-435 (decode) and :605-626 (prefill): query head h reads
 // KV head h / (H/KVH); s_t = (q.k_t)/sqrt(hd) for keys t <= pos; softmax; o = sum s_t v_t.
 // `window` > 0 restricts the keys to pos-window < t <= pos (0 = all keys).
+// `sink` != 0 adds one to the softmax's denominator: a key of score 0 that has no value
+// (the running maximum starts at 0 and the running sum at 1).
 #include "common.cuh"
 
 namespace {
@@ -22,7 +24,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attn_paged_kernel(T* out, const T* q, int q_stride,
                   const T* cache, const int* __restrict__ tables, int max_pages,
                   const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                  int n_tokens, int H, int KVH, int hd, int window, float scale) {
+                  int n_tokens, int H, int KVH, int hd, int window, float scale, int sink) {
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -45,7 +47,7 @@ attn_paged_kernel(T* out, const T* q, int q_stride,
     for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qr[d]);
     __syncwarp();
 
-    float m = -INFINITY, l = 0.f;
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[MAX_HD / 32];
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; i++) acc[i] = 0.f;
@@ -95,14 +97,14 @@ attn_paged_kernel(T* out, const T* q, int q_stride,
 template <typename T>
 int launch(T* out, const T* q, int q_stride, const T* cache, const int* tables, int max_pages,
            const int* tok_seq, const int* tok_pos, int n_tokens, int H, int KVH, int hd, int window,
-           float scale, cudaStream_t st) {
+           float scale, int sink, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > MAX_HD || (hd % 2) || H % KVH) return OE_ERR_UNSUPPORTED;
     const long long items = (long long)n_tokens * H;
     const long long blocks = (items + WARPS - 1) / WARPS;
     if (blocks > 2147483647LL) return OE_ERR_UNSUPPORTED;
     const int launch_rc = oe_launch(attn_paged_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), WARPS * hd * sizeof(float), st, 
-        out, q, q_stride, cache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, KVH, hd, window, scale);
+        out, q, q_stride, cache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, KVH, hd, window, scale, sink);
     return launch_rc;
 }
 
@@ -111,14 +113,14 @@ int launch(T* out, const T* q, int q_stride, const T* cache, const int* tables, 
 extern "C" {
 int oe_attn_paged_f32(float* out, const float* q, int q_stride, const float* cache, const int* tables,
                       int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H, int KVH,
-                      int hd, int window, float scale, cudaStream_t st) {
+                      int hd, int window, float scale, int sink, cudaStream_t st) {
     return launch<float>(out, q, q_stride, cache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, KVH, hd,
-                         window, scale, st);
+                         window, scale, sink, st);
 }
 int oe_attn_paged_bf16(bf16* out, const bf16* q, int q_stride, const bf16* cache, const int* tables,
                        int max_pages, const int* tok_seq, const int* tok_pos, int n_tokens, int H, int KVH,
-                       int hd, int window, float scale, cudaStream_t st) {
+                       int hd, int window, float scale, int sink, cudaStream_t st) {
     return launch<bf16>(out, q, q_stride, cache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, KVH, hd,
-                        window, scale, st);
+                        window, scale, sink, st);
 }
 }

@@ -34,6 +34,8 @@ LIBRARIES = {
     "gemm_simple": ("gemm_simple.cu", []),
     "attention": ("attention.cu", []),
     "sampling": ("sampling.cu", []),
+    "rowwise": ("rowwise.cu", []),
+    "recurrent": ("recurrent.cu", []),
     "gemm_tc": ("gemm_tcgen05.cu", []),
     "gemm_pair": ("gemm_tcgen05_pair.cu", []),
     "gemm_skinny": ("gemm_skinny.cu", []),

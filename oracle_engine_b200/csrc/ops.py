@@ -43,7 +43,23 @@ _SIGNATURES = {
         "oe_gemm_simple": [_P, _P, _P, _I, _I, _I, _L, _L, _I, _P],
     },
     "attention": {
-        "oe_attn_paged": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+        "oe_attn_paged": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    },
+    "rowwise": {
+        "oe_cast_rows_bf16": [_P, _P, _L, _P],
+        "oe_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _F, _P],
+        "oe_relu2": [_P, _L, _P],
+        "oe_tanh_rows": [_P, _P, _L, _P],
+        "oe_head_gate": [_P, _P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+        "oe_rot_norm_kv_write": [_P, _L, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    },
+    "recurrent": {
+        "oe_short_conv_prepare": [_P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+        "oe_conv_state_update": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
+        "oe_delta_rule_scan": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "oe_token_shift_mix": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
+        "oe_last_rows_to_state": [_P, _P, _I, _P, _P, _I, _P],
+        "oe_decay_scan": [_P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _P, _I, _I, _I, _P],
     },
     "sampling": {
         "oe_argmax_rows": [_P, _P, _I, _I, _P],
@@ -51,12 +67,15 @@ _SIGNATURES = {
         "oe_sample_rows": [_P, _P, _P, _I, _I, _F, _I, _F, _F, _I, _P, _P, _P, _P, _I, _I, _P],
     },
 }
-_TYPED = {"oe_embed_gather", "oe_rmsnorm", "oe_rope_kv_write", "oe_swiglu", "oe_gemm_simple", "oe_attn_paged"}
+_TYPED = {"oe_embed_gather", "oe_rmsnorm", "oe_rope_kv_write", "oe_swiglu", "oe_gemm_simple", "oe_attn_paged",
+          "oe_relu2", "oe_tanh_rows", "oe_rot_norm_kv_write", "oe_token_shift_mix", "oe_last_rows_to_state"}
 _fn_cache: dict[str, object] = {}
 
 
-def _fn(lib: str, name: str, dtype=None):
+def _fn(lib: str, name: str, dtype=None, in_dtype=None):
     full = f"{name}_{_SUFFIX[dtype]}" if name in _TYPED else name
+    if in_dtype is not None:                       # kernels typed by their input and their output
+        full = f"{name}_{_SUFFIX[in_dtype]}_{_SUFFIX[dtype]}"
     f = _fn_cache.get(full)
     if f is None:
         f = getattr(_build.load(lib), full)
@@ -209,10 +228,11 @@ def gemm_simple(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, accumulate:
 
 def attn_paged(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, tables: torch.Tensor,
                tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-               window: int, scale: float) -> None:
+               window: int, scale: float, sink: bool = False) -> None:
     """out[t] = attention of token t's query heads over keys (pos-window, pos] of its sequence.
 
-    q [T, >= H hd] (row stride free, e.g. a view of the qkv buffer), out [T, H hd]."""
+    q [T, >= H hd] (row stride free, e.g. a view of the qkv buffer), out [T, H hd].
+    sink: the softmax's denominator gets one added (a key of score 0 without a value)."""
     _dev(out, q, cache, tables, tok_seq, tok_pos)
     for t, n in ((tables, "tables"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
         _i32(t, n)
@@ -224,7 +244,196 @@ def attn_paged(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, tables: 
         raise KernelError("attn_paged: cache entry must be [pages, 2, KVH, PAGE, head_dim]")
     _check(_fn("attention", "oe_attn_paged", out.dtype)(
         _ptr(out), _ptr(q), q.stride(0), _ptr(cache), _ptr(tables), tables.shape[1], _ptr(tok_seq), _ptr(tok_pos),
-        T, n_heads, n_kv_heads, head_dim, int(window), float(scale), _stream()), "attn_paged")
+        T, n_heads, n_kv_heads, head_dim, int(window), float(scale), int(bool(sink)), _stream()), "attn_paged")
+
+
+# ---------------------------------------------------------------------------------------- rowwise.cu
+
+def _f32c(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.float32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous float32 tensor")
+
+
+def cast_rows(y: torch.Tensor, x: torch.Tensor) -> None:
+    """y = x (float32) rounded to bfloat16."""
+    _dev(y, x)
+    _f32c(x, "x")
+    if y.dtype != torch.bfloat16 or y.shape != x.shape or not y.is_contiguous():
+        raise KernelError("cast_rows: y must be contiguous bfloat16 of x's shape")
+    _check(_fn("rowwise", "oe_cast_rows_bf16")(_ptr(y), _ptr(x), x.numel(), _stream()), "cast_rows")
+
+
+def rmsnorm_add(dst: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, coef: float = 1.0) -> None:
+    """dst += coef * (y / sqrt(mean(y^2) + eps)) * w; all float32, rows of dst and y correspond."""
+    _dev(dst, y, w)
+    for t, n in ((dst, "dst"), (y, "y"), (w, "w")):
+        _f32c(t, n)
+    rows, D = y.shape
+    if dst.shape != y.shape or w.numel() != D:
+        raise KernelError("rmsnorm_add: dst of y's shape and w of its width expected")
+    _check(_fn("rowwise", "oe_rmsnorm_add")(_ptr(dst), _ptr(y), _ptr(w), rows, D, float(eps), float(coef), _stream()),
+           "rmsnorm_add")
+
+
+def relu2_(a: torch.Tensor) -> None:
+    """a = max(a, 0)^2 in place."""
+    _dev(a)
+    if not a.is_contiguous() or a.dtype not in _SUFFIX:
+        raise KernelError("relu2: a contiguous float32 or bfloat16 tensor expected")
+    _check(_fn("rowwise", "oe_relu2", a.dtype)(_ptr(a), a.numel(), _stream()), "relu2")
+
+
+def tanh_rows(y: torch.Tensor, x: torch.Tensor) -> None:
+    """y = tanh(x); x float32, y float32 or bfloat16."""
+    _dev(y, x)
+    _f32c(x, "x")
+    if y.shape != x.shape or not y.is_contiguous() or y.dtype not in _SUFFIX:
+        raise KernelError("tanh_rows: y must be contiguous, of x's shape")
+    _check(_fn("rowwise", "oe_tanh_rows", y.dtype)(_ptr(y), _ptr(x), x.numel(), _stream()), "tanh_rows")
+
+
+def head_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor | None, n_heads: int, dv: int,
+              norm: bool, act: str, eps: float = 0.0) -> None:
+    """out[t, h] = [o[t, h] / sqrt(mean(o[t, h]^2) + eps)] * [w] * act(gate[t, h]) for every head.
+
+    o and gate [T, >= H dv] of one dtype (row strides free), out contiguous [T, H dv]; w None, [dv]
+    (shared by the heads) or [H dv], float32; act "sigmoid" or "silu"."""
+    _dev(out, o, gate, w)
+    T = out.shape[0]
+    if out.shape[1] != n_heads * dv or not out.is_contiguous() or o.stride(1) != 1 or gate.stride(1) != 1 \
+            or o.dtype != gate.dtype or o.shape[1] < n_heads * dv or gate.shape[1] < n_heads * dv:
+        raise KernelError("head_gate: out contiguous [T, H dv]; o and gate of one dtype with at least H dv columns")
+    if (o.dtype, out.dtype) not in ((torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                    (torch.bfloat16, torch.bfloat16)):
+        raise KernelError(f"head_gate: no kernel for {o.dtype} -> {out.dtype}")
+    wmode = 0
+    if w is not None:
+        _f32c(w, "w")
+        wmode = 1 if w.numel() == dv and n_heads * dv != dv else (2 if w.numel() == n_heads * dv else -1)
+        if wmode < 0:
+            raise KernelError("head_gate: w must hold dv or H dv values")
+    _check(_fn("rowwise", "oe_head_gate", out.dtype, o.dtype)(
+        _ptr(out), _ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(w), T, n_heads, dv, int(bool(norm)), wmode,
+        {"sigmoid": 0, "silu": 1}[act], float(eps), _stream()), "head_gate")
+
+
+def rot_norm_kv_write(qk: torch.Tensor, inv_freq: torch.Tensor | None, rot_dims: int, cache: torch.Tensor | None,
+                      tables: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int,
+                      n_kv_heads: int, head_dim: int, eps: float, has_kv: bool) -> None:
+    """Rotates pairs (2i, 2i+1), i < rot_dims/2, of every q and k head by float(pos) * inv_freq[i], divides each head by
+    its root mean square (eps inside the root), and writes q back in place, k to the cache's key rows and the k
+    as projected to its value rows.  qk [T, >= (H + KVH) hd]; cache [pages, 2, KVH, PAGE, hd]."""
+    _dev(qk, inv_freq, cache, tables, tok_seq, tok_pos)
+    for t, n in ((tables, "tables"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
+        _i32(t, n)
+    width = (n_heads + (n_kv_heads if has_kv else 0)) * head_dim
+    if qk.shape[1] < width or qk.stride(1) != 1:
+        raise KernelError(f"rot_norm_kv_write: qk needs at least {width} contiguous columns")
+    if rot_dims:
+        _f32c(inv_freq, "inv_freq")
+        if inv_freq.numel() < rot_dims // 2:
+            raise KernelError("rot_norm_kv_write: inv_freq holds fewer values than rotated pairs")
+    if has_kv and (cache is None or cache.dtype != qk.dtype or not cache.is_contiguous()
+                   or tuple(cache.shape[1:]) != (2, n_kv_heads, PAGE, head_dim)):
+        raise KernelError("rot_norm_kv_write: cache entry must be [pages, 2, KVH, PAGE, head_dim] of qk's dtype")
+    _check(_fn("rowwise", "oe_rot_norm_kv_write", qk.dtype)(
+        _ptr(qk), qk.stride(0), _ptr(inv_freq), int(rot_dims), _ptr(cache), _ptr(tables), tables.shape[1],
+        _ptr(tok_seq), _ptr(tok_pos), qk.shape[0], n_heads, n_kv_heads, head_dim, float(eps), int(bool(has_kv)),
+        _stream()), "rot_norm_kv_write")
+
+
+# ---------------------------------------------------------------------------------------- recurrent.cu
+
+def short_conv_prepare(out_qkv, out_gb, proj, conv_w, conv_state, A_log, dt_bias, ctx, kv_heads: int, heads: int,
+                       dk: int, dv: int, q_scale: float) -> None:
+    """The inputs of a gated delta rule from the float32 projection rows [q | k | v | gate | beta | a]: see
+    csrc/recurrent.cu.  conv_w [C, taps], conv_state [slots, max(taps - 1, 1), C], C = 2 G dk + H dv."""
+    _dev(out_qkv, out_gb, proj, conv_w, conv_state, A_log, dt_bias)
+    for t, n in ((out_qkv, "out_qkv"), (out_gb, "out_gb"), (proj, "proj"), (conv_w, "conv_w"),
+                 (conv_state, "conv_state"), (A_log, "A_log"), (dt_bias, "dt_bias")):
+        _f32c(t, n)
+    T, P = proj.shape
+    C = 2 * kv_heads * dk + heads * dv
+    taps = conv_w.shape[1]
+    if P != C + heads * dv + 2 * heads or tuple(conv_w.shape) != (C, taps) or tuple(out_qkv.shape) != (T, C) \
+            or tuple(out_gb.shape) != (T, 2 * heads) or tuple(conv_state.shape[1:]) != (max(taps - 1, 1), C):
+        raise KernelError("short_conv_prepare: shapes do not agree")
+    _check(_fn("recurrent", "oe_short_conv_prepare")(
+        _ptr(out_qkv), _ptr(out_gb), _ptr(proj), P, _ptr(conv_w), taps, _ptr(conv_state), _ptr(A_log), _ptr(dt_bias),
+        _ptr(ctx.tok_seq), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), T, kv_heads, heads, dk, dv, float(q_scale), _stream()),
+        "short_conv_prepare")
+
+
+def conv_state_update(conv_state, proj, C: int, taps: int, ctx) -> None:
+    """conv_state[slot] = the last taps - 1 rows (first C columns) that the sequence has brought so far."""
+    _dev(conv_state, proj)
+    _f32c(conv_state, "conv_state")
+    _f32c(proj, "proj")
+    if taps <= 1:
+        return
+    _check(_fn("recurrent", "oe_conv_state_update")(_ptr(conv_state), _ptr(proj), proj.shape[1], C, taps,
+                                                    _ptr(ctx.seq_slot), _ptr(ctx.cu_q), ctx.n_seqs, _stream()),
+           "conv_state_update")
+
+
+def delta_rule_scan(o, state, qkv, gb, ctx, kv_heads: int, heads: int, dk: int, dv: int) -> None:
+    """Per sequence and head, over the step's tokens in order: S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  state [slots, H, dk, dv] float32 is read and written."""
+    _dev(o, state, qkv, gb)
+    for t, n in ((o, "o"), (state, "state"), (qkv, "qkv"), (gb, "gb")):
+        _f32c(t, n)
+    T = qkv.shape[0]
+    if tuple(state.shape[1:]) != (heads, dk, dv) or tuple(o.shape) != (T, heads * dv) \
+            or qkv.shape[1] != 2 * kv_heads * dk + heads * dv or tuple(gb.shape) != (T, 2 * heads):
+        raise KernelError("delta_rule_scan: shapes do not agree")
+    _check(_fn("recurrent", "oe_delta_rule_scan")(_ptr(o), _ptr(state), _ptr(qkv), _ptr(gb), _ptr(ctx.seq_slot),
+                                                  _ptr(ctx.cu_q), ctx.n_seqs, kv_heads, heads, dk, dv, _stream()),
+           "delta_rule_scan")
+
+
+def token_shift_mix(out, h, mu, prev_state, ctx) -> None:
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]; the row before a step's first row is prev_state[slot]."""
+    _dev(out, h, mu, prev_state)
+    _f32c(mu, "mu")
+    _f32c(prev_state, "prev_state")
+    T, D = h.shape
+    n_mix = mu.shape[0]
+    if tuple(out.shape) != (n_mix, T, D) or out.dtype != h.dtype or not (out.is_contiguous() and h.is_contiguous()) \
+            or mu.shape[1] != D or prev_state.shape[1] != D:
+        raise KernelError("token_shift_mix: shapes do not agree")
+    _check(_fn("recurrent", "oe_token_shift_mix", h.dtype)(
+        _ptr(out), _ptr(h), _ptr(mu), _ptr(prev_state), n_mix, T, D, _ptr(ctx.tok_seq), _ptr(ctx.seq_slot),
+        _ptr(ctx.cu_q), _stream()), "token_shift_mix")
+
+
+def last_rows_to_state(state, h, ctx) -> None:
+    """state[slot] = the sequence's last row of h in this step."""
+    _dev(state, h)
+    _f32c(state, "state")
+    if not h.is_contiguous() or state.shape[1] != h.shape[1]:
+        raise KernelError("last_rows_to_state: shapes do not agree")
+    _check(_fn("recurrent", "oe_last_rows_to_state", h.dtype)(_ptr(state), _ptr(h), h.shape[1], _ptr(ctx.seq_slot),
+                                                              _ptr(ctx.cu_q), ctx.n_seqs, _stream()),
+           "last_rows_to_state")
+
+
+def decay_scan(o, state, r, k, v, z, u, w0, ctx, heads: int, d: int) -> None:
+    """Per sequence and head, over the step's tokens in order: o = (S + diag(u) k v^T)^T r;
+    S <- diag(w) S + k v^T with w = exp(-exp(z + w0)).  r, k, v, z: float32 [T, H d] with one common row stride."""
+    _dev(o, state, r, k, v, z, u, w0)
+    for t, n in ((o, "o"), (state, "state"), (u, "u"), (w0, "w0")):
+        _f32c(t, n)
+    T = r.shape[0]
+    stride = r.stride(0)
+    for t in (r, k, v, z):
+        if t.dtype != torch.float32 or t.stride(1) != 1 or t.stride(0) != stride or tuple(t.shape) != (T, heads * d):
+            raise KernelError("decay_scan: r, k, v, z must be float32 [T, H d] with one row stride")
+    if tuple(state.shape[1:]) != (heads, d, d) or tuple(o.shape) != (T, heads * d) or u.numel() != heads * d \
+            or w0.numel() != heads * d:
+        raise KernelError("decay_scan: shapes do not agree")
+    _check(_fn("recurrent", "oe_decay_scan")(_ptr(o), _ptr(state), _ptr(r), _ptr(k), _ptr(v), _ptr(z), stride, _ptr(u),
+                                             _ptr(w0), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), ctx.n_seqs, heads, d,
+                                             _stream()), "decay_scan")
 
 
 _argmax_scratch: dict = {}

@@ -39,6 +39,16 @@ class Runtime:
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
+    def activations(self, x: torch.Tensor) -> torch.Tensor:
+        """The float32 residual stream as a sublayer's input: itself on the 32-bit path (the sublayer
+        must not write to it), rounded to bfloat16 otherwise."""
+        if self.dtype == torch.float32:
+            return x
+        from ..csrc import ops
+        y = self.empty(*x.shape)
+        ops.cast_rows(y, x)
+        return y
+
     def to_compute(self, t: torch.Tensor) -> torch.Tensor:
         """A stored matrix in the compute dtype (bf16 -> float32 is exact; a 32-bit
         matrix is rounded to bf16 only for the bf16 path)."""

@@ -1,6 +1,8 @@
 """Arrangements of a layer's parts.  `pre_norm`: x += mixer(norm(x)); x += ffn(norm(x)),
 the reference's layer (core/model.cpp:361-474).  The mixer and the feed-forward add their
-outputs into the float32 residual stream themselves (fused into their last product)."""
+outputs into the float32 residual stream themselves (fused into their last product).
+`norm_after`: x += norm(mixer(x)); x += norm(ffn(x)): the sublayers read the residual stream itself and
+their OUTPUT is normed before it is added; a sublayer adds its output into a zeroed float32 buffer."""
 from __future__ import annotations
 
 from .registry import BLOCKS
@@ -35,6 +37,37 @@ class PreNormBlock:
             self.feed_forward.forward(h, x, ctx)
         if rt is not None:
             rt.next_weights = None
+
+
+@BLOCKS.register("norm_after")
+class NormAfterBlock:
+    """x <- x + norm_1(mixer(x)); x <- x + norm_2(ffn(x)) (the second only with a feed-forward)."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm):
+        if mixer_norm is None or (feed_forward is not None and ffn_norm is None):
+            raise ValueError("norm_after: every sublayer needs the norm of its output")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.ffn_norm = ffn_norm
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ffn_norm) if p is not None]
+
+    def first_weights(self):
+        return _first_weights(self.mixer)
+
+    def forward(self, x, ctx, cache, state, owns_cache=True):
+        rt = self.mixer.rt
+        rt.next_weights = None
+        y = rt.empty(*x.shape, dtype=x.dtype)
+        y.zero_()
+        self.mixer.forward(rt.activations(x), y, ctx, cache, state, owns_cache)
+        self.mixer_norm.add_into(x, y)
+        if self.feed_forward is not None:
+            y.zero_()
+            self.feed_forward.forward(rt.activations(x), y, ctx)
+            self.ffn_norm.add_into(x, y)
 
 
 def _first_weights(part):

@@ -1,6 +1,7 @@
 """Feed-forward `swiglu`: g = Wg h, u = Wu h, a = g/(1+exp(-g)) * u, x += Wd a  (dense, no
 routing).  Reference: core/model.cpp:452-473 and :636-643.  The gate and up projections
-are fused into one matrix product at load ([Wg; Wu])."""
+are fused into one matrix product at load ([Wg; Wu]).
+Feed-forward `relu2`: a = max(Wu h, 0)^2, x += Wd a (dense, no gate)."""
 from __future__ import annotations
 
 import torch
@@ -62,3 +63,39 @@ class SwiGLU(Part):
             ops.swiglu(a, gu)
         matmul_nt(self.rt, residual, a, self.w_down, accumulate=True, early=chain_flags("ffn_out", T),
                   then=self.rt.next_weights)
+
+
+@FEED_FORWARDS.register("relu2")
+class SquaredReLU(Part):
+    graph_safe = True
+    """params: hidden_size, intermediate_size, tensor_names (optional overrides of "up" and "down")."""
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.D = int(self._need("hidden_size"))
+        self.FF = int(self._need("intermediate_size"))
+        names = {"up": "mlp.up_proj.weight", "down": "mlp.down_proj.weight", **self.params.get("tensor_names", {})}
+        self.names = {k: prefix + v for k, v in names.items()}
+        self.w_up = self.w_down = None
+
+    def tensors(self):
+        return [TensorDecl(self.names["up"], (self.FF, self.D)), TensorDecl(self.names["down"], (self.D, self.FF))]
+
+    def load(self, get):
+        self.w_up = self.rt.to_compute(get(self.names["up"]))
+        self.w_down = self.rt.to_compute(get(self.names["down"]))
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down) if t is not None)
+
+    def flops(self, start, count):
+        return count * 2.0 * 2 * self.D * self.FF
+
+    def first_weights(self):
+        return self.w_up
+
+    def forward(self, h, residual, ctx):
+        a = self.rt.empty(h.shape[0], self.FF)
+        matmul_nt(self.rt, a, h, self.w_up)
+        ops.relu2_(a)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True)

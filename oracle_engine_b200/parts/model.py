@@ -14,6 +14,7 @@ from .spec import ModelSpec, TensorDecl
 
 # importing the modules registers the built-in parts
 from . import attention, block, embedding, feedforward, norms, positions  # noqa: F401,E402
+from . import delta_rule, parallel, sink_attention, time_mix  # noqa: F401,E402
 
 
 class DecoderModel:
@@ -33,6 +34,7 @@ class DecoderModel:
         mparams = dict(ls.mixer.params)
         if isinstance(mparams.get("position"), str):
             mparams["position"] = self.positions[mparams["position"]]
+        mparams.setdefault("position_table", self.positions)      # for mixers that are made of mixers
         mixer = MIXERS.get(ls.mixer.kind)(mparams, ls.prefix, self.rt)
         ffn = None if ls.feed_forward is None else \
             FEED_FORWARDS.get(ls.feed_forward.kind)(ls.feed_forward.params, ls.prefix, self.rt)

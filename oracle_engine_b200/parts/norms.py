@@ -1,6 +1,8 @@
 """Norms.  `rms_norm`: y = (x / sqrt(mean(x^2) + eps)) * w on the float32 residual stream,
 computed in float32 and stored in the compute dtype (reference: core/ops.cpp:149-195; the
-epsilon is a parameter here, always passed)."""
+epsilon is a parameter here, always passed).  `add_into(dst, y, coef)` is the same norm applied to a
+sublayer's float32 OUTPUT and added, times coef, into another float32 tensor (layers that norm what
+a sublayer returns instead of what it reads)."""
 from __future__ import annotations
 
 from ..csrc import ops
@@ -33,3 +35,7 @@ class RMSNorm(Part):
         y = self.rt.empty(*x.shape)
         ops.rmsnorm(y, x, self.weight, self.eps)
         return y
+
+    def add_into(self, dst, y, coef: float = 1.0) -> None:
+        """dst += coef * norm(y); dst and y float32 of one shape."""
+        ops.rmsnorm_add(dst, y, self.weight, self.eps, coef)

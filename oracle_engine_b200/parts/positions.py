@@ -65,6 +65,29 @@ class Rotary(Part):
         return self.cos, self.sin
 
 
+@POSITIONS.register("rotary_pairs")
+class RotaryPairs(Part):
+    """Rotation of the pairs (2i, 2i+1), i < dims/2, of a head by position * base^(-2i/dims); dimensions
+    from `dims` on pass unchanged.  No table and no largest position: the kernel forms the angle as
+    float32(position) * float32(frequency) and takes its sine and cosine in float32.
+    params: dims, base."""
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.dims = int(self._need("dims"))
+        self.base = float(self._need("base"))
+        if self.dims % 2 or self.dims < 0:
+            raise ValueError(f"rotary_pairs: dims {self.dims} must be even")
+        self.inv_freq = None
+
+    def tables(self):
+        """(frequencies float32 [dims/2] on the device, dims)."""
+        if self.inv_freq is None:
+            f = [self.base ** (-(2.0 * i) / self.dims) for i in range(self.dims // 2)]
+            self.inv_freq = torch.tensor(f or [0.0], dtype=torch.float64).to(torch.float32).to(self.rt.device)
+        return self.inv_freq, self.dims
+
+
 @POSITIONS.register("none")
 class NoPosition(Part):
     """No position encoding: queries and keys are used as projected."""

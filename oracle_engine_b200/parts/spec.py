@@ -24,7 +24,7 @@ from typing import Any, Optional
 @dataclass(frozen=True)
 class TensorDecl:
     """A weight a part needs: full name in the file, shape, and how random weights fill it
-    ("normal": N(0, std); "ones_normal": 1 + N(0, norm_std))."""
+    ("normal": N(0, std); "ones_normal": 1 + N(0, norm_std)).  A size of -1 is one that only the file gives."""
     name: str
     shape: tuple[int, ...]
     init: str = "normal"

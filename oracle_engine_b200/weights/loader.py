@@ -19,7 +19,8 @@ from .safetensors_io import WeightError, kept_dtype
 
 
 def check_tensors(available: dict, decls, ignored_suffixes=()) -> None:
-    """available: name -> (dtype, shape).  Raises WeightError naming every problem."""
+    """available: name -> (dtype, shape).  Raises WeightError naming every problem.  A declared size of -1
+    is a size that only the file gives (the part reads it from the tensor it is handed)."""
     wanted = {d.name: tuple(d.shape) for d in decls}
     missing = sorted(n for n in wanted if n not in available)
     unexpected = sorted(n for n in available if n not in wanted
@@ -28,7 +29,7 @@ def check_tensors(available: dict, decls, ignored_suffixes=()) -> None:
     for n, shape in sorted(wanted.items()):
         if n in available:
             dt, have = available[n]
-            if tuple(have) != shape:
+            if len(have) != len(shape) or any(w >= 0 and w != h for w, h in zip(shape, have)):
                 wrong.append(f"{n}: file has {list(have)}, model needs {list(shape)}")
             elif not (dt.is_floating_point):
                 wrong.append(f"{n}: stored as {dt}, a floating-point tensor is needed")

@@ -84,6 +84,9 @@ class RandomSource:
 
     def read(self, name) -> torch.Tensor:
         d = self.decls[name]
+        if any(int(n) < 0 for n in d.shape):
+            raise ValueError(f"{name}: a size that only a file gives cannot be filled with random weights; "
+                             f"give it in the configuration")
         if d.init == "ones_normal":
             return normal_tensor(self.seed, name, d.shape, 1.0, self.norm_std, self.dtype, self.device)
         if d.init == "normal":
