@@ -196,3 +196,14 @@ class PlainFuvipel:
             if layers_out is not None:
                 layers_out.append(x.clone())
         return (rms(x, eps) * W["final.norm"]) @ W["embed"].T
+
+    def logits(self, tokens):
+        return self.forward(tokens)
+
+
+def generate(model, prompt, n):
+    """n greedy tokens (first maximum), recomputing the whole sequence for each."""
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(torch.argmax(model.forward(seq)[-1]).item()))
+    return seq[len(prompt):]
