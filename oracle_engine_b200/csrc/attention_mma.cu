@@ -54,6 +54,8 @@ struct AttnArgs {
     int* counters;             // [B * KVH] zeros (n_splits > 1)
     int stages;                // K/V tiles staged ahead: 2 (double buffer) or 1
     int cluster;               // warps kernel: CTAs (a thread-block cluster) that share one (sequence, KV head)
+    int sink;                  // != 0: one is added to the softmax's denominator (a key of score 0 without a value);
+                               // only the kernel that reads rotated queries (attn_mma_kernel, not fused) and the merge
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -344,7 +346,9 @@ attn_mma_kernel(const AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             if (!valid[i]) continue;
-            const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+            // the sink weighs 2^(0 - m) beside the keys' weights 2^(s - m)
+            const float l_all = l_run[i] + (a.sink ? exp2f(m_run[i] == -INFINITY ? 0.f : -m_run[i]) : 0.f);
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
             bf16* o = a.out + (packed0 + tok[i]) * (long long)(a.H * HD) + (size_t)head[i] * HD + tig * 2;
 #pragma unroll
             for (int n = 0; n < HD / 8; n++)
@@ -797,7 +801,7 @@ attn_decode_warps_kernel(const AttnArgs a) {
 
 // out[row, head] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits taken in order.
 __global__ void attn_merge_kernel(bf16* out, const float* partial,
-                                  const int* __restrict__ tok_seq, int H, int n_splits) {
+                                  const int* __restrict__ tok_seq, int H, int n_splits, int sink) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -807,9 +811,9 @@ __global__ void attn_merge_kernel(bf16* out, const float* partial,
         return;
     }
     const float* p = partial + ((size_t)t * H + h) * n_splits * (HD + 2);
-    float m = -INFINITY;
+    float m = sink ? 0.f : -INFINITY;                      // the sink: a split of score 0, weight 1 and no value
     for (int s = 0; s < n_splits; s++) m = fmaxf(m, p[s * (HD + 2) + HD]);
-    float l = 0.f;
+    float l = sink ? exp2f(-m) : 0.f;
     for (int s = 0; s < n_splits; s++) {
         const float ms = p[s * (HD + 2) + HD];
         if (ms != -INFINITY) l += p[s * (HD + 2) + HD + 1] * exp2f(ms - m);
@@ -879,7 +883,7 @@ long long oe_attn_mma_partial_floats(int n_tokens, int H, int n_splits) {
 int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* cache, const int* tables, int max_pages,
                      const int* cu_q, const int* seq_start, const int* seq_qlen, const int* tok_seq, int n_seqs,
                      int n_tokens, int max_qlen, int H, int KVH, int window, float scale, int n_splits, float* partial,
-                     cudaStream_t st) {
+                     int sink, cudaStream_t st) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (H % KVH || ((uintptr_t)q & 3) || (q_stride & 1)) return OE_ERR_UNSUPPORTED;
     const int G = H / KVH;
@@ -890,7 +894,7 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = partial;
     a.fused = 0; a.cos_tab = nullptr; a.sin_tab = nullptr; a.cache_w = nullptr; a.counters = nullptr;
-    a.stages = 2; a.cluster = 1;
+    a.stages = 2; a.cluster = 1; a.sink = sink;
     // rows per sequence tile: 16 per warp; few rows (decode) use fewer warps
     const long long rows_needed = (long long)max_qlen * G;
     int nwarps = rows_needed <= 16 ? 1 : (rows_needed <= 32 ? 2 : 4);
@@ -907,7 +911,7 @@ int oe_attn_mma_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* c
     else rc = launch<4>(a, n_seqs, grid_x, st);
     if (rc) return rc;
     if (a.n_splits > 1) {
-        const int launch_rc = oe_launch(attn_merge_kernel, dim3(n_tokens, H), dim3(HD >= 128 ? 128 : 64), 0, st, out, partial, tok_seq, H, a.n_splits);
+        const int launch_rc = oe_launch(attn_merge_kernel, dim3(n_tokens, H), dim3(HD >= 128 ? 128 : 64), 0, st, out, partial, tok_seq, H, a.n_splits, sink);
         rc = launch_rc;
     }
     return rc;
@@ -936,7 +940,7 @@ int oe_attn_decode_fused_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     int nwarps = G <= 16 ? 1 : (G <= 32 ? 2 : 4);
     a.tokens_per_tile = (nwarps * 16) / G;
     a.n_splits = n_splits < 1 ? 1 : n_splits;
-    a.stages = nwarps == 1 ? decode_stages(a.n_splits) : 2; a.cluster = 1;
+    a.stages = nwarps == 1 ? decode_stages(a.n_splits) : 2; a.cluster = 1; a.sink = 0;
     if (nwarps == 1) return launch<1>(a, n_seqs, a.n_splits, st);
     if (nwarps == 2) return launch<2>(a, n_seqs, a.n_splits, st);
     return launch<4>(a, n_seqs, a.n_splits, st);
@@ -961,7 +965,7 @@ int oe_attn_decode_warps_bf16(bf16* out, const bf16* qkv, long long qkv_stride, 
     a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen; a.H = H; a.KVH = KVH; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.partial = nullptr; a.fused = 1; a.cos_tab = cos_tab; a.sin_tab = sin_tab; a.cache_w = has_kv ? cache : nullptr;
-    a.counters = nullptr; a.tokens_per_tile = 1; a.n_splits = 1; a.stages = 2;
+    a.counters = nullptr; a.tokens_per_tile = 1; a.n_splits = 1; a.stages = 2; a.sink = 0;
     if (cluster < 1 || cluster > 8) return OE_ERR_UNSUPPORTED;
     a.cluster = cluster;
     if (shape == 0) shape = 6 * 16 + 2;
@@ -1030,7 +1034,7 @@ int oe_attn_mma_bf16_noalloc(bf16* out, const bf16* q, long long q_stride, const
         g_noalloc_addr[dev] = p;
     }
     return oe_attn_mma_bf16(out, q, q_stride, cache, tables, max_pages, cu_q, seq_start, seq_qlen, tok_seq, n_seqs,
-                            n_tokens, max_qlen, H, KVH, window, scale, n_splits, g_noalloc_addr[dev], stream);
+                            n_tokens, max_qlen, H, KVH, window, scale, n_splits, g_noalloc_addr[dev], 0, stream);
 }
 
 const char* oe_attn_mma_error_string(int code) {

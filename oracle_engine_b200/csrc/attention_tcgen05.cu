@@ -75,6 +75,7 @@ struct Args {
     int H, KVH, window;
     float scale_log2;
     int tokens_per_tile;
+    int sink;                  // != 0: one is added to the softmax's denominator (a key of score 0 without a value)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -367,7 +368,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int tok = r / G, head = kvh * G + r % G;
         const bool valid = active && tok < nt;
         const int pos = start + t0 + tok;
-        float m_run = -INFINITY, l_run = 0.f;              // m_run in units of the scaled scores (log2)
+        // m_run in units of the scaled scores (log2).  With a sink the maximum starts at the sink's score, 0,
+        // and the sum holds the sink's weight 2^(0 - m_run) from the first block on.
+        float m_run = a.sink ? 0.f : -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int i = 0; i < n_blocks && active; i++) {
             ok = mbar_wait(&ctl->s_full[i & 1], (uint32_t)(i >> 1) & 1u, ctl, 6);
@@ -404,6 +407,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2);
             if (i == 0) {
                 m_run = m_new;
+                if (a.sink) l_run = fast_exp2(-m_new);
             } else if (__any_sync(0xffffffffu, valid && m_new > m_run + RESCALE_STEP)) {
                 // (only the tile's own rows vote: the scores of the rows past them are whatever shared memory held)
                 // P_{i-1} V_{i-1} must have been added to O before O is rescaled.  S_i is complete, so
@@ -515,7 +519,7 @@ int oe_attn_tc_head_dim() { return HD; }
 // rows (q_stride a multiple of 8) and G = H/KVH <= 128.
 int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* cache, long long n_pages, const int* tables,
                     int max_pages, const int* cu_q, const int* seq_start, const int* seq_qlen, int n_seqs, int n_tokens,
-                    int max_qlen, int H, int KVH, int window, float scale, cudaStream_t st) {
+                    int max_qlen, int H, int KVH, int window, float scale, int sink, cudaStream_t st) {
     if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (H % KVH || (q_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15)) return OE_ERR_UNSUPPORTED;
     const int G = H / KVH;
@@ -526,6 +530,7 @@ int oe_attn_tc_bf16(bf16* out, const bf16* q, long long q_stride, const bf16* ca
     a.out = out; a.tables = tables; a.max_pages = max_pages; a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen;
     a.H = H; a.KVH = KVH; a.window = window; a.scale_log2 = scale * 1.4426950408889634f;
     a.tokens_per_tile = BM / G;
+    a.sink = sink;
     CUtensorMap map_q, map_kv;
     {   // q as [token][head][dim]; a box holds 64 dims of the G heads of tokens_per_tile tokens
         cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)H, (cuuint64_t)n_tokens};

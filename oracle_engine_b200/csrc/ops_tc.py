@@ -261,7 +261,7 @@ def _attn_lib(head_dim: int):
         lib = _build.load("attention_tc", {"OE_HD": head_dim})
         lib.oe_attn_mma_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                         c_void_p, c_void_p]
+                                         c_void_p, c_int, c_void_p]
         lib.oe_attn_mma_bf16.restype = c_int
         lib.oe_attn_decode_fused_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -286,7 +286,8 @@ def _attn_tc5_lib(head_dim: int):
     if lib is None:
         lib = _build.load("attention_tc5", {"OE_HD": head_dim})
         lib.oe_attn_tc_bf16.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p,
-                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                        c_void_p]
         lib.oe_attn_tc_bf16.restype = c_int
         lib.oe_attn_tc_error.argtypes = []
         lib.oe_attn_tc_error.restype = c_int
@@ -342,8 +343,9 @@ def _decode_ctas_per_sm(head_dim: int) -> int:
 
 
 def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int,
-              scale: float) -> None:
+              scale: float, sink: bool = False) -> None:
     """out[t] = attention of the step's tokens over their sequences' paged cache (bfloat16).
+    sink: one is added to the softmax's denominator (a key of score 0 that has no value).
 
     qkv [T, >= H hd] (queries first), out [T, H hd], cache [pages, 2, KVH, PAGE, hd]."""
     T = out.shape[0]
@@ -360,7 +362,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
         code = _attn_tc5_lib(head_dim).oe_attn_tc_bf16(
             out.data_ptr(), qkv.data_ptr(), qkv.stride(0), cache.data_ptr(), cache.shape[0], tables.data_ptr(),
             tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, T,
-            ctx.max_qlen, n_heads, n_kv_heads, int(window), float(scale), ops._stream())
+            ctx.max_qlen, n_heads, n_kv_heads, int(window), float(scale), int(bool(sink)), ops._stream())
         ops._check(code, "attention_tcgen05")
         return
     lib = _attn_lib(head_dim)
@@ -374,7 +376,7 @@ def attention(out, qkv, cache, tables, ctx, n_heads: int, n_kv_heads: int, head_
                                 tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(),
                                 ctx.seq_qlen.data_ptr(), ctx.tok_seq.data_ptr(), ctx.n_seqs, T, max(1, ctx.max_qlen),
                                 n_heads, n_kv_heads, int(window), float(scale), n_splits,
-                                None if partial is None else partial.data_ptr(),
+                                None if partial is None else partial.data_ptr(), int(bool(sink)),
                                 ops._stream())
     ops._check(code, "attention_mma", {"splits": n_splits})
     if n_splits > 1:

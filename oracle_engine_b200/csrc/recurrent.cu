@@ -10,9 +10,9 @@
 //   last_rows_to_state   a sequence's last row of the step, kept for the next step
 //   decay_scan           o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T, w = exp(-exp(z + w0))
 //
-// Both scans give column j of a head's S to thread j: the columns never mix, so a thread keeps its
-// column in registers for all tokens of the step, and the vectors every column needs (k, q, r, w)
-// go through shared memory a few tokens at a time.  A step's tokens of one sequence are walked in
+// Both scans give column j of a head's S to a few adjacent threads (each a share of its rows): the columns
+// never mix, so the threads keep their column in registers for all tokens of the step, and the vectors
+// every column needs (k, q, r, w) go through shared memory a few tokens at a time.  A step's tokens of one sequence are walked in
 // order, whatever their number: a prompt, a piece of one and a single token run the same
 // instructions in the same order, so the cut of a sequence into steps changes no bit.
 #include "common.cuh"
@@ -98,34 +98,43 @@ conv_state_update_kernel(float* conv_state, const float* proj, int P, int C, int
     }
 }
 
-// grid (H, B); thread j owns column j of S[dk][dv] of head blockIdx.x of sequence blockIdx.y.
-// qkv row [q: G*dk | k: G*dk | v: H*dv], gb row [g: H | beta: H]; o [T, H*dv] float32.
-template <int DK>
-__global__ void __launch_bounds__(256)
+// Sum over the L adjacent lanes that share a column (L a power of two up to 8), the same order everywhere.
+template <int L>
+__device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
+    for (int o = 1; o < L; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// grid (H, B).  Column j of S[dk][dv] of head blockIdx.x of sequence blockIdx.y belongs to the L adjacent
+// threads j*L .. j*L+L-1; thread l of them keeps rows l*PER .. l*PER+PER-1 in registers (dk = L * per,
+// per <= PER).  qkv row [q: G*dk | k: G*dk | v: H*dv], gb row [g: H | beta: H]; o [T, H*dv] float32.
+template <int PER, int L>
+__global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb,
                        const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
                        int G, int H, int dk, int dv) {
-    __shared__ float kq[CHUNK][2][DK];
+    __shared__ float kq[CHUNK][2][PER * L];
     __shared__ float sc[CHUNK][2];
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x / L, l = threadIdx.x % L;
     const int slot = seq_slot[b];
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
     const int g = h / (H / G);
     const int C = 2 * G * dk + H * dv;
+    const int per = dk / L, i0 = l * per;
     const bool mine = j < dv;
     float* S = state + (((size_t)slot * H + h) * dk) * dv;
-    float s[DK];
+    float s[PER];
 #pragma unroll
-    for (int i = 0; i < DK; i++) s[i] = (mine && i < dk) ? S[(size_t)i * dv + j] : 0.f;
+    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)(i0 + i) * dv + j] : 0.f;
     for (int c0 = 0; c0 < n; c0 += CHUNK) {
         const int cn = min(CHUNK, n - c0);
         __syncthreads();
         for (int e = threadIdx.x; e < cn * 2 * dk; e += blockDim.x) {
-            const int tt = e / (2 * dk), r = e % (2 * dk), which = r / dk, d = r % dk;
-            // which 0: k, 1: q
+            const int tt = e / (2 * dk), r = e % (2 * dk), which = r / dk, d = r % dk;      // which 0: k, 1: q
             kq[tt][which][d] = qkv[(size_t)(row0 + c0 + tt) * C + (size_t)(which == 0 ? G + g : g) * dk + d];
         }
         if (threadIdx.x < cn * 2) {
@@ -133,27 +142,30 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
             sc[tt][w] = gb[(size_t)(row0 + c0 + tt) * 2 * H + (size_t)w * H + h];
         }
         __syncthreads();
-        if (!mine) continue;
         for (int tt = 0; tt < cn; tt++) {
             const size_t row = (size_t)(row0 + c0 + tt);
             const float decay = sc[tt][0], beta = sc[tt][1];
-            const float v = qkv[row * C + (size_t)2 * G * dk + (size_t)h * dv + j];
+            const float v = mine ? qkv[row * C + (size_t)2 * G * dk + (size_t)h * dv + j] : 0.f;
+            const float* kk = &kq[tt][0][i0];
+            const float* qq = &kq[tt][1][i0];
             float dot = 0.f;
 #pragma unroll
-            for (int i = 0; i < DK; i++)
-                if (i < dk) { s[i] *= decay; dot = fmaf(kq[tt][0][i], s[i], dot); }
+            for (int i = 0; i < PER; i++)
+                if (i < per) { s[i] *= decay; dot = fmaf(kk[i], s[i], dot); }
+            dot = lanes_sum<L>(dot);
             const float u = beta * (v - dot);
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < DK; i++)
-                if (i < dk) { s[i] = fmaf(kq[tt][0][i], u, s[i]); acc = fmaf(kq[tt][1][i], s[i], acc); }
-            o[row * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
+            for (int i = 0; i < PER; i++)
+                if (i < per) { s[i] = fmaf(kk[i], u, s[i]); acc = fmaf(qq[i], s[i], acc); }
+            acc = lanes_sum<L>(acc);
+            if (mine && l == 0) o[row * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
         }
     }
     if (mine) {
 #pragma unroll
-        for (int i = 0; i < DK; i++)
-            if (i < dk) S[(size_t)i * dv + j] = s[i];
+        for (int i = 0; i < PER; i++)
+            if (i < per) S[(size_t)(i0 + i) * dv + j] = s[i];
     }
 }
 
@@ -193,26 +205,26 @@ last_rows_to_state_kernel(float* state, const T* h, int D, const int* __restrict
     for (int d = threadIdx.x; d < D; d += blockDim.x) state[(size_t)slot * D + d] = to_f32(h[(size_t)last * D + d]);
 }
 
-// grid (H, B); thread j owns column j of S[d][d].  r, k, v, z: float32 rows of H*d with their own strides;
-// u, w0: [H*d].
-template <int DK>
-__global__ void __launch_bounds__(256)
+// grid (H, B); column j of S[d][d] belongs to L adjacent threads as in the delta rule's scan.  r, k, v, z:
+// float32 rows of H*d with one row stride; u, w0: [H*d].
+template <int PER, int L>
+__global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 decay_scan_kernel(float* o, float* state, const float* r, const float* k, const float* v, const float* z,
                   long long stride, const float* __restrict__ u, const float* __restrict__ w0,
                   const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int H, int d) {
-    __shared__ float vec[CHUNK][3][DK];          // r, u*k... per token: 0 r, 1 k, 2 w
-    __shared__ float uk[CHUNK][DK];
+    __shared__ float vec[CHUNK][4][PER * L];          // per token: 0 r, 1 k, 2 w, 3 u*k
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x / L, l = threadIdx.x % L;
     const int slot = seq_slot[b];
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
+    const int per = d / L, i0 = l * per;
     const bool mine = j < d;
     float* S = state + (((size_t)slot * H + h) * d) * d;
-    float s[DK];
+    float s[PER];
 #pragma unroll
-    for (int i = 0; i < DK; i++) s[i] = (mine && i < d) ? S[(size_t)i * d + j] : 0.f;
+    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)(i0 + i) * d + j] : 0.f;
     for (int c0 = 0; c0 < n; c0 += CHUNK) {
         const int cn = min(CHUNK, n - c0);
         __syncthreads();
@@ -223,29 +235,41 @@ decay_scan_kernel(float* o, float* state, const float* r, const float* k, const 
             vec[tt][0][i] = r[at];
             vec[tt][1][i] = kk;
             vec[tt][2][i] = expf(-expf(z[at] + w0[(size_t)h * d + i]));
-            uk[tt][i] = u[(size_t)h * d + i] * kk;
+            vec[tt][3][i] = u[(size_t)h * d + i] * kk;
         }
         __syncthreads();
-        if (!mine) continue;
         for (int tt = 0; tt < cn; tt++) {
             const size_t row = (size_t)(row0 + c0 + tt);
-            const float vj = v[row * stride + (size_t)h * d + j];
+            const float vj = mine ? v[row * stride + (size_t)h * d + j] : 0.f;
+            const float* rr = &vec[tt][0][i0];
+            const float* kk = &vec[tt][1][i0];
+            const float* ww = &vec[tt][2][i0];
+            const float* uk = &vec[tt][3][i0];
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < DK; i++) {
-                if (i < d) {
-                    acc = fmaf(vec[tt][0][i], fmaf(uk[tt][i], vj, s[i]), acc);
-                    s[i] = fmaf(vec[tt][2][i], s[i], vec[tt][1][i] * vj);
+            for (int i = 0; i < PER; i++) {
+                if (i < per) {
+                    acc = fmaf(rr[i], fmaf(uk[i], vj, s[i]), acc);
+                    s[i] = fmaf(ww[i], s[i], kk[i] * vj);
                 }
             }
-            o[row * (size_t)(H * d) + (size_t)h * d + j] = acc;
+            acc = lanes_sum<L>(acc);
+            if (mine && l == 0) o[row * (size_t)(H * d) + (size_t)h * d + j] = acc;
         }
     }
     if (mine) {
 #pragma unroll
-        for (int i = 0; i < DK; i++)
-            if (i < d) S[(size_t)i * d + j] = s[i];
+        for (int i = 0; i < PER; i++)
+            if (i < per) S[(size_t)(i0 + i) * d + j] = s[i];
     }
+}
+
+// Lanes per column: the most of 8, 4, 2, 1 that divide the rows, leave each lane 8 rows or more and keep
+// the block within 512 threads (256 where a lane keeps 64 rows or more in registers).
+inline int lanes_per_column(int rows, int cols) {
+    for (int L = 8; L > 1; L >>= 1)
+        if (rows % L == 0 && rows / L >= 8 && cols * L <= (rows / L > 32 ? 256 : 512)) return L;
+    return 1;
 }
 
 inline int round_up_warp(int n) { return (n + 31) / 32 * 32; }
@@ -281,11 +305,16 @@ int oe_delta_rule_scan(float* o, float* state, const float* qkv, const float* gb
                        int n_seqs, int G, int H, int dk, int dv, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (dk < 1 || dk > 256 || dv < 1 || dv > 256 || G < 1 || H % G || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
-    const dim3 grid(H, n_seqs), block(round_up_warp(dv));
-#define OE_DELTA(DK) \
-    if (dk <= DK) return oe_launch(delta_rule_scan_kernel<DK>, grid, block, 0, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv);
-    OE_DELTA(16) OE_DELTA(32) OE_DELTA(64) OE_DELTA(128) OE_DELTA(256)
-#undef OE_DELTA
+    const int L = lanes_per_column(dk, dv), per = dk / L;
+    const dim3 grid(H, n_seqs), block(round_up_warp(dv * L));
+    if (block.x > (per > 32 ? 256u : 512u)) return OE_ERR_UNSUPPORTED;
+#define OE_SCAN(PER, LL) \
+    if (L == LL && per <= PER) return oe_launch(delta_rule_scan_kernel<PER, LL>, grid, block, 0, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv);
+    OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
+    OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
+    OE_SCAN(8, 2) OE_SCAN(16, 2) OE_SCAN(32, 2) OE_SCAN(64, 2) OE_SCAN(128, 2)
+    OE_SCAN(8, 1) OE_SCAN(16, 1) OE_SCAN(32, 1) OE_SCAN(64, 1) OE_SCAN(128, 1) OE_SCAN(256, 1)
+#undef OE_SCAN
     return OE_ERR_UNSUPPORTED;
 }
 
@@ -318,11 +347,16 @@ int oe_decay_scan(float* o, float* state, const float* r, const float* k, const 
                   cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (d < 1 || d > 256 || H < 1 || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
-    const dim3 grid(H, n_seqs), block(round_up_warp(d));
-#define OE_DECAY(DK) \
-    if (d <= DK) return oe_launch(decay_scan_kernel<DK>, grid, block, 0, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d);
-    OE_DECAY(16) OE_DECAY(32) OE_DECAY(64) OE_DECAY(128) OE_DECAY(256)
-#undef OE_DECAY
+    const int L = lanes_per_column(d, d), per = d / L;
+    const dim3 grid(H, n_seqs), block(round_up_warp(d * L));
+    if (block.x > (per > 32 ? 256u : 512u)) return OE_ERR_UNSUPPORTED;
+#define OE_SCAN(PER, LL) \
+    if (L == LL && per <= PER) return oe_launch(decay_scan_kernel<PER, LL>, grid, block, 0, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d);
+    OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
+    OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
+    OE_SCAN(8, 2) OE_SCAN(16, 2) OE_SCAN(32, 2) OE_SCAN(64, 2) OE_SCAN(128, 2)
+    OE_SCAN(8, 1) OE_SCAN(16, 1) OE_SCAN(32, 1) OE_SCAN(64, 1) OE_SCAN(128, 1) OE_SCAN(256, 1)
+#undef OE_SCAN
     return OE_ERR_UNSUPPORTED;
 }
 

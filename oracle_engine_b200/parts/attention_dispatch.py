@@ -40,10 +40,10 @@ def rope_and_cache(rt, qkv, cos, sin, cache, ctx, H, KVH, hd, owns_cache) -> Non
 
 
 def attend(rt, out, qkv, cache, ctx, H, KVH, hd, window, scale, sink: bool = False) -> None:
-    """sink: the softmax's denominator gets one added (csrc/attention.cu)."""
-    if rt.dtype == torch.bfloat16 and rt.tensor_cores and not sink:
+    """sink: the softmax's denominator gets one added (a key of score 0 without a value), in every kernel."""
+    if rt.dtype == torch.bfloat16 and rt.tensor_cores:
         from ..csrc import ops_tc
         if ops_tc.attention_supported(hd, H, KVH):
-            ops_tc.attention(out, qkv, cache.kv, cache.tables, ctx, H, KVH, hd, window, scale)
+            ops_tc.attention(out, qkv, cache.kv, cache.tables, ctx, H, KVH, hd, window, scale, sink)
             return
     ops.attn_paged(out, qkv, cache.kv, cache.tables, ctx.tok_seq, ctx.tok_pos, H, KVH, hd, window, scale, sink)

@@ -157,6 +157,24 @@ def test_far_keys_and_page_borders_under_a_peaked_softmax(models, tmp_path, dtyp
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_head_sizes(tmp_path, dtype):
+    """Head sizes 128 and 64 at a width of 1,024: in bfloat16 the prompts go through the tensor-core products and
+    the tensor-memory attention, decoding through the kernel that splits the keys; states of 128 x 128."""
+    folder = fm.write(tmp_path / "m", fm.REAL, 31, std=0.05)
+    plain = pf.PlainFuvipel(folder)
+    lens = [333, 70, 200]
+    requests = [helpers.random_tokens(n, 1000, 800 + i) for i, n in enumerate(lens)]
+    eng = _engine(folder, dtype, max_tokens=2048)
+    runs = {"batched": helpers.batched_steps(requests, [n - 6 for n in lens], 3),
+            "pieces": helpers.piece_steps(requests, [helpers.cut(n, [150, 2, 100]) for n in lens], batch_size=1)}
+    for k, steps in runs.items():
+        got = helpers.collect(steps, helpers.TraceRunner(eng, tmp_path / k).run(steps), requests)
+        _compare(got, plain, requests, TOL[dtype], f"REAL {dtype} {k}")
+    eng.check_device_errors()
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_slots_and_pages_are_used_again(models, tmp_path, dtype):
     """Two slots for six requests: a request that starts in a slot another left reads nothing of it."""
     folder, plain = models["F1"]
