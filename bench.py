@@ -6,6 +6,8 @@
     python bench.py --shape 8b --workload baseline      # 32 prompts of 128..4,096 tokens, 256 steps
     python bench.py --profile [--batch 64]              # device time per kind of kernel, on standard error
     python bench.py --impl reference --steps K          # the reference's own benchmark program (CPU)
+    python bench.py --design fuvipel [--widths 1024,2048,3072] [--profile]
+                                                        # the Fuvipel design beside a Llama of equal width and depth
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default
 8), timed on the device with CUDA events over exactly K decode steps after W warm-up
@@ -353,6 +355,77 @@ def profile_decode(engine, lengths, vocab, file):
                 engine.free(s)
 
 
+def fuvipel_shape(width: int, layers: int, vocab: int) -> dict:
+    """A Fuvipel of real layer sizes: three gated-delta layers, then a parallel layer, repeated; heads of 128
+    (key, value and attention) and of 64 (time mixing), a feed-forward of 4 x width on every layer."""
+    heads = width // 128
+    delta = {"type": "delta", "mlp": {"kind": "dense", "ff": 4 * width},
+             "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": 4 * width},
+           "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                              "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 500000.0}},
+                     "right": {"heads": width // 64, "dim": 64, "rank": 64}}}
+    return {"architecture": "Fuvipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [par if i % 4 == 3 else delta for i in range(layers)]}
+
+
+def llama_shape(width: int, layers: int, vocab: int) -> dict:
+    """The Llama decoder of the same width, depth and vocabulary: heads of 128, four query heads to a key head,
+    a SwiGLU of 8/3 x width (the same weights as a two-matrix feed-forward of 4 x width)."""
+    heads = width // 128
+    return dict(LLAMA_3B, vocab_size=vocab, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=(8 * width // 3 + 63) // 64 * 64,
+                rope_scaling=None, bos_token_id=1, eos_token_id=2, max_position_embeddings=8192)
+
+
+def design_compare(args) -> int:
+    """Prefill and decode throughput of the Fuvipel design beside the Llama decoder at equal width, depth and
+    vocabulary (random weights), one JSON line; with --profile the device time per kind of kernel instead."""
+    import torch
+    from oracle_engine_b200 import LlamaConfig
+    from oracle_engine_b200.config.fuvipel import FuvipelConfig
+    from oracle_engine_b200.engine.engine import Engine
+    pk = peaks()
+    layers, vocab, context = args.layers or 8, 32000, 1024
+    sizes = {}
+    for width in [int(w) for w in args.widths.split(",")]:
+        row = {}
+        for name, cfg in (("fuvipel", FuvipelConfig.from_dict(fuvipel_shape(width, layers, vocab))),
+                          ("llama", LlamaConfig.from_dict(llama_shape(width, layers, vocab)))):
+            engine = Engine.from_config(cfg, seed=SEED, dtype=args.dtype, max_tokens=64 * context + 4096,
+                                        max_seq_len=4096, n_slots=64)
+            if args.profile:
+                print(f"==== {name}, width {width}, {layers} layers", file=sys.stderr)
+                profile_decode(engine, [PREFILL_TOKENS], vocab, sys.stderr)
+                profile_decode(engine, [PROMPT_LEN] * args.batch, vocab, sys.stderr)
+                del engine
+                torch.cuda.empty_cache()
+                continue
+            ms, fl = time_prefill(engine, [PREFILL_TOKENS], vocab, runs=5, warmup=3, settle_ms=args.settle_ms)
+            out = {"prefill_tok_s": round(PREFILL_TOKENS / (ms / 1e3), 1), "prefill_ms": round(ms, 3),
+                   "prefill_frac_of_bf16_peak": round(fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "weights_gb": round(engine.model.step_bytes([]) / 1e9, 3)}
+            ms8, _ = time_prefill(engine, [PROMPT_LEN] * 8, vocab, runs=5, warmup=3, settle_ms=args.settle_ms)
+            out["prefill_8x%d_tok_s" % PROMPT_LEN] = round(8 * PROMPT_LEN / (ms8 / 1e3), 1)
+            out["prefill_8x%d_ms" % PROMPT_LEN] = round(ms8, 3)
+            for b in (8, 64):
+                d = time_decode(engine, [PROMPT_LEN] * b, min(args.steps, 64), args.warmup, vocab, 3, args.settle_ms)
+                out[f"decode_b{b}_tok_s"] = round(d["tok_s"], 1)
+                out[f"decode_b{b}_ms"] = round(d["ms_per_step"], 4)
+                out[f"decode_b{b}_frac_of_hbm"] = round(d["step_bytes"] / (d["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+                out[f"decode_b{b}_launches_per_step"] = d["launches"] // min(args.steps, 64)
+            row[name] = out
+            del engine
+            torch.cuda.empty_cache()
+        sizes[str(width)] = row
+    if not args.profile:
+        print(json.dumps({"design": "fuvipel beside llama at equal width, depth and vocabulary", "layers": layers,
+                          "vocab": vocab, "dtype": args.dtype, "prefill_tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
+                          "peaks": pk, "data": "synthetic token ids, random-init weights N(0, 0.02) from seed 2",
+                          "sizes": sizes}))
+    return 0
+
+
 def reference_arm(args) -> int:
     """Runs the reference's own benchmark program (benchmark/bench_engine.cpp, compiled unmodified
     by baseline/build_reference.py into baseline/_ref/) on the benchmark model: the Llama 3.2 3B
@@ -465,8 +538,14 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="print device time per kind of kernel of a prompt step and a decode step on standard error, "
                          "and nothing else")
+    ap.add_argument("--design", default=None, choices=["fuvipel"],
+                    help="measure this design beside the Llama decoder at equal sizes instead of the headline workload")
+    ap.add_argument("--widths", default="1024,2048,3072", help="model widths of --design")
     args = ap.parse_args()
 
+    if args.design and args.impl == "ours" and args.gpus == 1:
+        args.warmup = max(args.warmup, 3)
+        return design_compare(args)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:

@@ -47,7 +47,7 @@ _SIGNATURES = {
     },
     "rowwise": {
         "oe_cast_rows_bf16": [_P, _P, _L, _P],
-        "oe_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _F, _P],
+        "oe_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _F, _I, _P, _P],
         "oe_relu2": [_P, _L, _P],
         "oe_tanh_rows": [_P, _P, _L, _P],
         "oe_head_gate": [_P, _P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _P],
@@ -263,16 +263,22 @@ def cast_rows(y: torch.Tensor, x: torch.Tensor) -> None:
     _check(_fn("rowwise", "oe_cast_rows_bf16")(_ptr(y), _ptr(x), x.numel(), _stream()), "cast_rows")
 
 
-def rmsnorm_add(dst: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, coef: float = 1.0) -> None:
-    """dst += coef * (y / sqrt(mean(y^2) + eps)) * w; all float32, rows of dst and y correspond."""
-    _dev(dst, y, w)
+def rmsnorm_add(dst: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, coef: float = 1.0,
+                accumulate: bool = True, cast_out: torch.Tensor | None = None) -> None:
+    """dst (+)= coef * (y / sqrt(mean(y^2) + eps)) * w; all float32, rows of dst and y correspond.
+    accumulate False: dst is written without being read.  cast_out: a contiguous bfloat16 tensor of dst's
+    shape that receives the new dst, rounded."""
+    _dev(dst, y, w, cast_out)
+    if cast_out is not None and (cast_out.dtype != torch.bfloat16 or cast_out.shape != dst.shape
+                                 or not cast_out.is_contiguous()):
+        raise KernelError("rmsnorm_add: cast_out must be contiguous bfloat16 of dst's shape")
     for t, n in ((dst, "dst"), (y, "y"), (w, "w")):
         _f32c(t, n)
     rows, D = y.shape
     if dst.shape != y.shape or w.numel() != D:
         raise KernelError("rmsnorm_add: dst of y's shape and w of its width expected")
-    _check(_fn("rowwise", "oe_rmsnorm_add")(_ptr(dst), _ptr(y), _ptr(w), rows, D, float(eps), float(coef), _stream()),
-           "rmsnorm_add")
+    _check(_fn("rowwise", "oe_rmsnorm_add")(_ptr(dst), _ptr(y), _ptr(w), rows, D, float(eps), float(coef),
+                                            int(bool(accumulate)), _ptr(cast_out), _stream()), "rmsnorm_add")
 
 
 def relu2_(a: torch.Tensor) -> None:

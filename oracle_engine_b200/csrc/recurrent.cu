@@ -20,59 +20,83 @@
 namespace {
 
 constexpr int MAX_TAPS = 16;
-constexpr int CHUNK = 8;            // tokens whose vectors are staged at once
+constexpr int MAX_CHUNK = 16;       // tokens whose vectors are staged at once (fewer where they are long)
+
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// proj row: [q: G*dk | k: G*dk | v: H*dv | gate: H*dv | beta: H | a: H]; one block per token.
+// proj row: [q: G*dk | k: G*dk | v: H*dv | gate: H*dv | beta: H | a: H].  grid (tokens, 2 G + value chunks):
+// block y < 2 G takes one q or k head (convolution, silu, unit vector), the others VCHUNK value channels each;
+// block y == 0 also writes the token's decays and step sizes.
 // out_qkv row [q | k | v] (C = 2 G dk + H dv), out_gb row [g: H | beta: H].
-__global__ void __launch_bounds__(256)
+constexpr int VCHUNK = 256;
+__device__ __forceinline__ float conv_silu(const float* proj, int P, const float* __restrict__ conv_w, int taps,
+                                           const float* st, int C, int t, int rel, int c) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; j++) {
+        const int r = rel - (taps - 1) + j;
+        const float x = r >= 0 ? proj[(size_t)(t - rel + r) * P + c] : st[(size_t)(rel + j) * C + c];
+        acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+    }
+    return silu_f(acc);
+}
+
+__global__ void __launch_bounds__(128)
 short_conv_prepare_kernel(float* out_qkv, float* out_gb, const float* proj, int P,
                           const float* __restrict__ conv_w, int taps, const float* conv_state,
                           const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                           const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                           const int* __restrict__ cu_q, int G, int H, int dk, int dv, float q_scale) {
-    extern __shared__ float act[];              // the token's q and k after convolution and silu
+    __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, part = blockIdx.y;
     const int b = tok_seq[t];
     if (b < 0) return;
     const int slot = seq_slot[b];
     const int rel = t - cu_q[b];                // index of the token among its sequence's tokens of this step
     const int nqk = 2 * G * dk, C = nqk + H * dv;
     const float* st = conv_state + (size_t)slot * (taps - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < taps; j++) {
-            const int r = rel - (taps - 1) + j;
-            const float x = r >= 0 ? proj[(size_t)(t - rel + r) * P + c] : st[(size_t)(rel + j) * C + c];
-            acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
-        }
-        const float y = silu_f(acc);
-        if (c < nqk) act[c] = y;
-        else out_qkv[(size_t)t * C + c] = y;
-    }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int hh = warp; hh < 2 * G; hh += nwarps) {
-        const float* a = act + (size_t)hh * dk;
+    if (part < 2 * G) {
+        // dk <= 256: a thread keeps its (up to two) channels in registers
+        const int c0 = part * dk;
+        float y[2] = {0.f, 0.f};
         float ss = 0.f;
-        for (int d = lane; d < dk; d += 32) ss = fmaf(a[d], a[d], ss);
-        ss = warp_sum(ss);
-        const float s = (1.f / sqrtf(ss + 1e-6f)) * (hh < G ? q_scale : 1.f);
-        for (int d = lane; d < dk; d += 32) out_qkv[(size_t)t * C + (size_t)hh * dk + d] = a[d] * s;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int d = threadIdx.x + e * 128;
+            if (d < dk) { y[e] = conv_silu(proj, P, conv_w, taps, st, C, t, rel, c0 + d); ss = fmaf(y[e], y[e], ss); }
+        }
+        ss = block_sum(ss, red);
+        const float s = (1.f / sqrtf(ss + 1e-6f)) * (part < G ? q_scale : 1.f);
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int d = threadIdx.x + e * 128;
+            if (d < dk) out_qkv[(size_t)t * C + c0 + d] = y[e] * s;
+        }
+    } else {
+        const int c0 = nqk + (part - 2 * G) * VCHUNK;
+        for (int c = c0 + threadIdx.x; c < min(c0 + VCHUNK, C); c += 128)
+            out_qkv[(size_t)t * C + c] = conv_silu(proj, P, conv_w, taps, st, C, t, rel, c);
     }
-    const float* row = proj + (size_t)t * P;
-    for (int hh = threadIdx.x; hh < H; hh += blockDim.x) {
-        const float bt = row[C + H * dv + hh], a = row[C + H * dv + H + hh];
-        out_gb[(size_t)t * 2 * H + hh] = expf(-expf(A_log[hh]) * softplus_f(a + dt_bias[hh]));
-        out_gb[(size_t)t * 2 * H + H + hh] = 1.f / (1.f + expf(-bt));
+    if (part == 0) {
+        const float* row = proj + (size_t)t * P;
+        for (int hh = threadIdx.x; hh < H; hh += blockDim.x) {
+            const float bt = row[C + H * dv + hh], a = row[C + H * dv + H + hh];
+            out_gb[(size_t)t * 2 * H + hh] = expf(-expf(A_log[hh]) * softplus_f(a + dt_bias[hh]));
+            out_gb[(size_t)t * 2 * H + H + hh] = 1.f / (1.f + expf(-bt));
+        }
     }
 }
 
-// One block per sequence; a thread owns whole channels, so it reads a channel's old rows before it writes them.
+// grid (sequences, channel chunks); a thread owns whole channels, so it reads a channel's old rows before it
+// writes them.
 __global__ void __launch_bounds__(256)
 conv_state_update_kernel(float* conv_state, const float* proj, int P, int C, int taps,
                          const int* __restrict__ seq_slot, const int* __restrict__ cu_q) {
@@ -83,19 +107,19 @@ conv_state_update_kernel(float* conv_state, const float* proj, int P, int C, int
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
     float* st = conv_state + (size_t)slot * (taps - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float keep[MAX_TAPS];
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    if (c >= C) return;
+    float keep[MAX_TAPS];
 #pragma unroll
-        for (int i = 0; i < MAX_TAPS; i++) {
-            if (i < taps - 1) {
-                const int r = n - (taps - 1) + i;
-                keep[i] = r >= 0 ? proj[(size_t)(row0 + r) * P + c] : st[(size_t)(n + i) * C + c];
-            }
+    for (int i = 0; i < MAX_TAPS; i++) {
+        if (i < taps - 1) {
+            const int r = n - (taps - 1) + i;
+            keep[i] = r >= 0 ? proj[(size_t)(row0 + r) * P + c] : st[(size_t)(n + i) * C + c];
         }
-#pragma unroll
-        for (int i = 0; i < MAX_TAPS; i++)
-            if (i < taps - 1) st[(size_t)i * C + c] = keep[i];
     }
+#pragma unroll
+    for (int i = 0; i < MAX_TAPS; i++)
+        if (i < taps - 1) st[(size_t)i * C + c] = keep[i];
 }
 
 // Sum over the L adjacent lanes that share a column (L a power of two up to 8), the same order everywhere.
@@ -106,66 +130,115 @@ __device__ __forceinline__ float lanes_sum(float v) {
     return v;
 }
 
-// grid (H, B).  Column j of S[dk][dv] of head blockIdx.x of sequence blockIdx.y belongs to the L adjacent
-// threads j*L .. j*L+L-1; thread l of them keeps rows l*PER .. l*PER+PER-1 in registers (dk = L * per,
-// per <= PER).  qkv row [q: G*dk | k: G*dk | v: H*dv], gb row [g: H | beta: H]; o [T, H*dv] float32.
+// Which row of its column lane l keeps in register ii: with one lane the rows in order; with L lanes
+// groups of four consecutive rows dealt round robin, so that the lanes of a column read consecutive 16-byte
+// pieces of a staged vector.
+template <int L>
+__device__ __forceinline__ int lane_row(int ii, int l) { return L == 1 ? ii : ((ii >> 2) * 4 * L + 4 * l + (ii & 3)); }
+
+// grid (H * column tiles, B).  A block owns `cols` columns of S[dk][dv] of one head of one sequence; column j
+// belongs to L adjacent threads, thread l of them keeps dk / L rows in registers (lane_row).  The step's
+// tokens are walked in order in chunks: while one chunk is computed, the next chunk's k, q (dk each), the
+// block's v columns, the decay and the step size arrive in shared memory by asynchronous copies.
+// qkv row [q: G*dk | k: G*dk | v: H*dv], gb row [g: H | beta: H]; o [T, H*dv] float32.
 template <int PER, int L>
 __global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb,
                        const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
-                       int G, int H, int dk, int dv) {
-    __shared__ float kq[CHUNK][2][PER * L];
-    __shared__ float sc[CHUNK][2];
+                       int G, int H, int dk, int dv, int cols, int chunk) {
+    extern __shared__ __align__(16) float stage_mem[];
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x / L, l = threadIdx.x % L;
+    const int tiles = (dv + cols - 1) / cols;
+    const int h = blockIdx.x / tiles, col0 = (blockIdx.x % tiles) * cols, b = blockIdx.y;
+    const int jj = threadIdx.x / L, l = threadIdx.x % L, j = col0 + jj;
     const int slot = seq_slot[b];
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
     const int g = h / (H / G);
     const int C = 2 * G * dk + H * dv;
-    const int per = dk / L, i0 = l * per;
-    const bool mine = j < dv;
+    const int per = dk / L;
+    const bool mine = jj < cols && j < dv;
+    const int tokf = (2 * dk + cols + 2 + 3) / 4 * 4;            // floats of a staged token: k, q, v columns, g, beta
     float* S = state + (((size_t)slot * H + h) * dk) * dv;
     float s[PER];
 #pragma unroll
-    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)(i0 + i) * dv + j] : 0.f;
-    for (int c0 = 0; c0 < n; c0 += CHUNK) {
-        const int cn = min(CHUNK, n - c0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < cn * 2 * dk; e += blockDim.x) {
-            const int tt = e / (2 * dk), r = e % (2 * dk), which = r / dk, d = r % dk;      // which 0: k, 1: q
-            kq[tt][which][d] = qkv[(size_t)(row0 + c0 + tt) * C + (size_t)(which == 0 ? G + g : g) * dk + d];
-        }
-        if (threadIdx.x < cn * 2) {
-            const int tt = threadIdx.x / 2, w = threadIdx.x % 2;
-            sc[tt][w] = gb[(size_t)(row0 + c0 + tt) * 2 * H + (size_t)w * H + h];
-        }
-        __syncthreads();
-        for (int tt = 0; tt < cn; tt++) {
+    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)lane_row<L>(i, l) * dv + j] : 0.f;
+
+    auto issue = [&](int c0, float* dst) {
+        const int cn = min(chunk, n - c0);
+        for (int e = threadIdx.x; e < cn * tokf; e += blockDim.x) {
+            const int tt = e / tokf, r = e % tokf;
             const size_t row = (size_t)(row0 + c0 + tt);
-            const float decay = sc[tt][0], beta = sc[tt][1];
-            const float v = mine ? qkv[row * C + (size_t)2 * G * dk + (size_t)h * dv + j] : 0.f;
-            const float* kk = &kq[tt][0][i0];
-            const float* qq = &kq[tt][1][i0];
-            float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < PER; i++)
-                if (i < per) { s[i] *= decay; dot = fmaf(kk[i], s[i], dot); }
-            dot = lanes_sum<L>(dot);
-            const float u = beta * (v - dot);
-            float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < PER; i++)
-                if (i < per) { s[i] = fmaf(kk[i], u, s[i]); acc = fmaf(qq[i], s[i], acc); }
-            acc = lanes_sum<L>(acc);
-            if (mine && l == 0) o[row * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
+            const float* src = nullptr;
+            if (r < dk) src = qkv + row * C + (size_t)(G + g) * dk + r;
+            else if (r < 2 * dk) src = qkv + row * C + (size_t)g * dk + (r - dk);
+            else if (r < 2 * dk + cols) { if (col0 + r - 2 * dk < dv) src = qkv + row * C + (size_t)2 * G * dk + (size_t)h * dv + col0 + (r - 2 * dk); }
+            else if (r < 2 * dk + cols + 2) src = gb + row * 2 * H + (size_t)(r - 2 * dk - cols) * H + h;
+            if (src) cp_async4(dst + e, src);
         }
+        cp_async_commit();
+    };
+    const int stagef = chunk * tokf;
+    issue(0, stage_mem);
+    int buf = 0;
+    for (int c0 = 0; c0 < n; c0 += chunk, buf ^= 1) {
+        const int cn = min(chunk, n - c0);
+        if (c0 + chunk < n) { issue(c0 + chunk, stage_mem + (buf ^ 1) * stagef); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        const float* base = stage_mem + buf * stagef;
+        for (int tt = 0; tt < cn; tt++) {
+            const float* tk = base + tt * tokf;
+            const float decay = tk[2 * dk + cols], beta = tk[2 * dk + cols + 1];
+            const float v = tk[2 * dk + (jj < cols ? jj : 0)];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            if (L == 1) {
+#pragma unroll
+                for (int i = 0; i < PER; i++)
+                    if (i < per) { s[i] *= decay; d0 = fmaf(tk[i], s[i], d0); }
+            } else {
+                const float4* k4 = reinterpret_cast<const float4*>(tk);
+#pragma unroll
+                for (int i = 0; i < PER; i += 4) {
+                    if (i < per) {
+                        const float4 kv = k4[(i >> 2) * L + l];
+                        s[i] *= decay; s[i + 1] *= decay; s[i + 2] *= decay; s[i + 3] *= decay;
+                        d0 = fmaf(kv.x, s[i], d0); d1 = fmaf(kv.y, s[i + 1], d1);
+                        d2 = fmaf(kv.z, s[i + 2], d2); d3 = fmaf(kv.w, s[i + 3], d3);
+                    }
+                }
+            }
+            const float dot = lanes_sum<L>((d0 + d1) + (d2 + d3));
+            const float u = beta * (v - dot);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (L == 1) {
+#pragma unroll
+                for (int i = 0; i < PER; i++)
+                    if (i < per) { s[i] = fmaf(tk[i], u, s[i]); a0 = fmaf(tk[dk + i], s[i], a0); }
+            } else {
+                const float4* k4 = reinterpret_cast<const float4*>(tk);
+                const float4* q4 = reinterpret_cast<const float4*>(tk + dk);
+#pragma unroll
+                for (int i = 0; i < PER; i += 4) {
+                    if (i < per) {
+                        const float4 kv = k4[(i >> 2) * L + l], qv = q4[(i >> 2) * L + l];
+                        s[i] = fmaf(kv.x, u, s[i]); s[i + 1] = fmaf(kv.y, u, s[i + 1]);
+                        s[i + 2] = fmaf(kv.z, u, s[i + 2]); s[i + 3] = fmaf(kv.w, u, s[i + 3]);
+                        a0 = fmaf(qv.x, s[i], a0); a1 = fmaf(qv.y, s[i + 1], a1);
+                        a2 = fmaf(qv.z, s[i + 2], a2); a3 = fmaf(qv.w, s[i + 3], a3);
+                    }
+                }
+            }
+            const float acc = lanes_sum<L>((a0 + a1) + (a2 + a3));
+            if (mine && l == 0) o[(size_t)(row0 + c0 + tt) * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
+        }
+        __syncthreads();
     }
     if (mine) {
 #pragma unroll
         for (int i = 0; i < PER; i++)
-            if (i < per) S[(size_t)(i0 + i) * dv + j] = s[i];
+            if (i < per) S[(size_t)lane_row<L>(i, l) * dv + j] = s[i];
     }
 }
 
@@ -205,74 +278,119 @@ last_rows_to_state_kernel(float* state, const T* h, int D, const int* __restrict
     for (int d = threadIdx.x; d < D; d += blockDim.x) state[(size_t)slot * D + d] = to_f32(h[(size_t)last * D + d]);
 }
 
-// grid (H, B); column j of S[d][d] belongs to L adjacent threads as in the delta rule's scan.  r, k, v, z:
-// float32 rows of H*d with one row stride; u, w0: [H*d].
+// grid (H * column tiles, B), columns and lanes as in the delta rule's scan.  Staged per token: r, k, the
+// decay's argument z (turned into w = exp(-exp(z + w0)) once it has arrived), u * k, and the block's v columns.
+// r, k, v, z: float32 rows of H*d with one row stride; u, w0: [H*d].
 template <int PER, int L>
 __global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 decay_scan_kernel(float* o, float* state, const float* r, const float* k, const float* v, const float* z,
                   long long stride, const float* __restrict__ u, const float* __restrict__ w0,
-                  const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int H, int d) {
-    __shared__ float vec[CHUNK][4][PER * L];          // per token: 0 r, 1 k, 2 w, 3 u*k
+                  const int* __restrict__ seq_slot, const int* __restrict__ cu_q, int H, int d, int cols, int chunk) {
+    extern __shared__ __align__(16) float stage_mem[];
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x / L, l = threadIdx.x % L;
+    const int tiles = (d + cols - 1) / cols;
+    const int h = blockIdx.x / tiles, col0 = (blockIdx.x % tiles) * cols, b = blockIdx.y;
+    const int jj = threadIdx.x / L, l = threadIdx.x % L, j = col0 + jj;
     const int slot = seq_slot[b];
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
-    const int per = d / L, i0 = l * per;
-    const bool mine = j < d;
+    const int per = d / L;
+    const bool mine = jj < cols && j < d;
+    const int dp = (d + 3) / 4 * 4;
+    const int tokf = 4 * dp + (cols + 3) / 4 * 4;                // r, k, z -> w, u * k, v columns
     float* S = state + (((size_t)slot * H + h) * d) * d;
     float s[PER];
 #pragma unroll
-    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)(i0 + i) * d + j] : 0.f;
-    for (int c0 = 0; c0 < n; c0 += CHUNK) {
-        const int cn = min(CHUNK, n - c0);
+    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)lane_row<L>(i, l) * d + j] : 0.f;
+
+    auto issue = [&](int c0, float* dst) {
+        const int cn = min(chunk, n - c0);
+        for (int e = threadIdx.x; e < cn * tokf; e += blockDim.x) {
+            const int tt = e / tokf, q = e % tokf, which = q / dp, i = q % dp;
+            const size_t at = (size_t)(row0 + c0 + tt) * stride + (size_t)h * d;
+            const float* src = nullptr;
+            if (which < 3) { if (i < d) src = (which == 0 ? r : which == 1 ? k : z) + at + i; }
+            else if (which == 4) { if (i < cols && col0 + i < d) src = v + at + col0 + i; }
+            if (src) cp_async4(dst + e, src);
+        }
+        cp_async_commit();
+    };
+    const int stagef = chunk * tokf;
+    issue(0, stage_mem);
+    int buf = 0;
+    for (int c0 = 0; c0 < n; c0 += chunk, buf ^= 1) {
+        const int cn = min(chunk, n - c0);
+        if (c0 + chunk < n) { issue(c0 + chunk, stage_mem + (buf ^ 1) * stagef); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
         __syncthreads();
+        float* base = stage_mem + buf * stagef;
         for (int e = threadIdx.x; e < cn * d; e += blockDim.x) {
             const int tt = e / d, i = e % d;
-            const size_t at = (size_t)(row0 + c0 + tt) * stride + (size_t)h * d + i;
-            const float kk = k[at];
-            vec[tt][0][i] = r[at];
-            vec[tt][1][i] = kk;
-            vec[tt][2][i] = expf(-expf(z[at] + w0[(size_t)h * d + i]));
-            vec[tt][3][i] = u[(size_t)h * d + i] * kk;
+            float* tk = base + tt * tokf;
+            tk[2 * dp + i] = expf(-expf(tk[2 * dp + i] + w0[(size_t)h * d + i]));
+            tk[3 * dp + i] = u[(size_t)h * d + i] * tk[dp + i];
         }
         __syncthreads();
         for (int tt = 0; tt < cn; tt++) {
-            const size_t row = (size_t)(row0 + c0 + tt);
-            const float vj = mine ? v[row * stride + (size_t)h * d + j] : 0.f;
-            const float* rr = &vec[tt][0][i0];
-            const float* kk = &vec[tt][1][i0];
-            const float* ww = &vec[tt][2][i0];
-            const float* uk = &vec[tt][3][i0];
-            float acc = 0.f;
+            const float* tk = base + tt * tokf;
+            const float vj = tk[4 * dp + (jj < cols ? jj : 0)];
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (L == 1) {
 #pragma unroll
-            for (int i = 0; i < PER; i++) {
-                if (i < per) {
-                    acc = fmaf(rr[i], fmaf(uk[i], vj, s[i]), acc);
-                    s[i] = fmaf(ww[i], s[i], kk[i] * vj);
+                for (int i = 0; i < PER; i++) {
+                    if (i < per) {
+                        a0 = fmaf(tk[i], fmaf(tk[3 * dp + i], vj, s[i]), a0);
+                        s[i] = fmaf(tk[2 * dp + i], s[i], tk[dp + i] * vj);
+                    }
+                }
+            } else {
+                const float4* r4 = reinterpret_cast<const float4*>(tk);
+                const float4* k4 = reinterpret_cast<const float4*>(tk + dp);
+                const float4* w4 = reinterpret_cast<const float4*>(tk + 2 * dp);
+                const float4* uk4 = reinterpret_cast<const float4*>(tk + 3 * dp);
+#pragma unroll
+                for (int i = 0; i < PER; i += 4) {
+                    if (i < per) {
+                        const int at = (i >> 2) * L + l;
+                        const float4 rv = r4[at], kv = k4[at], wv = w4[at], uv = uk4[at];
+                        a0 = fmaf(rv.x, fmaf(uv.x, vj, s[i]), a0); a1 = fmaf(rv.y, fmaf(uv.y, vj, s[i + 1]), a1);
+                        a2 = fmaf(rv.z, fmaf(uv.z, vj, s[i + 2]), a2); a3 = fmaf(rv.w, fmaf(uv.w, vj, s[i + 3]), a3);
+                        s[i] = fmaf(wv.x, s[i], kv.x * vj); s[i + 1] = fmaf(wv.y, s[i + 1], kv.y * vj);
+                        s[i + 2] = fmaf(wv.z, s[i + 2], kv.z * vj); s[i + 3] = fmaf(wv.w, s[i + 3], kv.w * vj);
+                    }
                 }
             }
-            acc = lanes_sum<L>(acc);
-            if (mine && l == 0) o[row * (size_t)(H * d) + (size_t)h * d + j] = acc;
+            const float acc = lanes_sum<L>((a0 + a1) + (a2 + a3));
+            if (mine && l == 0) o[(size_t)(row0 + c0 + tt) * (size_t)(H * d) + (size_t)h * d + j] = acc;
         }
+        __syncthreads();
     }
     if (mine) {
 #pragma unroll
         for (int i = 0; i < PER; i++)
-            if (i < per) S[(size_t)(i0 + i) * d + j] = s[i];
+            if (i < per) S[(size_t)lane_row<L>(i, l) * d + j] = s[i];
     }
 }
 
-// Lanes per column: the most of 8, 4, 2, 1 that divide the rows, leave each lane 8 rows or more and keep
-// the block within 512 threads (256 where a lane keeps 64 rows or more in registers).
-inline int lanes_per_column(int rows, int cols) {
+// How a scan is laid out: lanes per column (the most of 8, 4, 2 that leave each lane a multiple of four rows
+// and at least eight, else 1), columns per block (32, or all where a lane keeps 64 rows or more), tokens per
+// staged chunk (the most of 16, 8, 4, 2, 1 whose two stages fit 48 KB).
+struct ScanPlan { int L, cols, threads, chunk; size_t smem; };
+inline ScanPlan scan_plan(int rows, int ncols, int tok_floats_without_cols, int pad_cols) {
+    ScanPlan p;
+    p.L = 1;
     for (int L = 8; L > 1; L >>= 1)
-        if (rows % L == 0 && rows / L >= 8 && cols * L <= (rows / L > 32 ? 256 : 512)) return L;
-    return 1;
+        if (rows % (4 * L) == 0 && rows / L >= 8) { p.L = L; break; }
+    p.cols = ncols < 32 ? ncols : 32;
+    while (p.cols * p.L > (rows / p.L > 32 ? 256 : 512)) p.cols /= 2;
+    p.threads = (p.cols * p.L + 31) / 32 * 32;
+    const int tokf = pad_cols ? tok_floats_without_cols + (p.cols + 3) / 4 * 4 : (tok_floats_without_cols + p.cols + 3) / 4 * 4;
+    p.chunk = MAX_CHUNK;
+    while (p.chunk > 1 && (size_t)2 * p.chunk * tokf * sizeof(float) > 48 * 1024) p.chunk /= 2;
+    p.smem = (size_t)2 * p.chunk * tokf * sizeof(float);
+    return p;
 }
-
-inline int round_up_warp(int n) { return (n + 31) / 32 * 32; }
 
 }  // namespace
 
@@ -284,13 +402,10 @@ int oe_short_conv_prepare(float* out_qkv, float* out_gb, const float* proj, int 
                           cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (taps < 1 || taps > MAX_TAPS || G < 1 || H % G) return OE_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)2 * G * dk * sizeof(float);
-    if (smem > 200 * 1024) return OE_ERR_UNSUPPORTED;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(short_conv_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    return oe_launch(short_conv_prepare_kernel, dim3(n_tokens), dim3(256), smem, st, out_qkv, out_gb, proj, P, conv_w, taps,
+    if (dk > 256) return OE_ERR_UNSUPPORTED;
+    const int parts = 2 * G + (H * dv + VCHUNK - 1) / VCHUNK;
+    if (parts > 65535) return OE_ERR_UNSUPPORTED;
+    return oe_launch(short_conv_prepare_kernel, dim3(n_tokens, parts), dim3(128), 0, st, out_qkv, out_gb, proj, P, conv_w, taps,
                      conv_state, A_log, dt_bias, tok_seq, seq_slot, cu_q, G, H, dk, dv, q_scale);
 }
 
@@ -298,18 +413,19 @@ int oe_conv_state_update(float* conv_state, const float* proj, int P, int C, int
                          const int* cu_q, int n_seqs, cudaStream_t st) {
     if (n_seqs <= 0 || taps <= 1) return 0;
     if (taps > MAX_TAPS) return OE_ERR_UNSUPPORTED;
-    return oe_launch(conv_state_update_kernel, dim3(n_seqs), dim3(256), 0, st, conv_state, proj, P, C, taps, seq_slot, cu_q);
+    return oe_launch(conv_state_update_kernel, dim3(n_seqs, (C + 255) / 256), dim3(256), 0, st, conv_state, proj, P, C, taps, seq_slot, cu_q);
 }
 
 int oe_delta_rule_scan(float* o, float* state, const float* qkv, const float* gb, const int* seq_slot, const int* cu_q,
                        int n_seqs, int G, int H, int dk, int dv, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (dk < 1 || dk > 256 || dv < 1 || dv > 256 || G < 1 || H % G || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
-    const int L = lanes_per_column(dk, dv), per = dk / L;
-    const dim3 grid(H, n_seqs), block(round_up_warp(dv * L));
-    if (block.x > (per > 32 ? 256u : 512u)) return OE_ERR_UNSUPPORTED;
+    const ScanPlan p = scan_plan(dk, dv, 2 * dk + 2, 0);
+    if (p.cols < 1 || p.smem > 48 * 1024) return OE_ERR_UNSUPPORTED;
+    const int L = p.L, per = dk / L;
+    const dim3 grid(H * ((dv + p.cols - 1) / p.cols), n_seqs), block(p.threads);
 #define OE_SCAN(PER, LL) \
-    if (L == LL && per <= PER) return oe_launch(delta_rule_scan_kernel<PER, LL>, grid, block, 0, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv);
+    if (L == LL && per <= PER) return oe_launch(delta_rule_scan_kernel<PER, LL>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk);
     OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
     OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
     OE_SCAN(8, 2) OE_SCAN(16, 2) OE_SCAN(32, 2) OE_SCAN(64, 2) OE_SCAN(128, 2)
@@ -347,11 +463,12 @@ int oe_decay_scan(float* o, float* state, const float* r, const float* k, const 
                   cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (d < 1 || d > 256 || H < 1 || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
-    const int L = lanes_per_column(d, d), per = d / L;
-    const dim3 grid(H, n_seqs), block(round_up_warp(d * L));
-    if (block.x > (per > 32 ? 256u : 512u)) return OE_ERR_UNSUPPORTED;
+    const ScanPlan p = scan_plan(d, d, 4 * ((d + 3) / 4 * 4), 1);
+    if (p.cols < 1 || p.smem > 48 * 1024) return OE_ERR_UNSUPPORTED;
+    const int L = p.L, per = d / L;
+    const dim3 grid(H * ((d + p.cols - 1) / p.cols), n_seqs), block(p.threads);
 #define OE_SCAN(PER, LL) \
-    if (L == LL && per <= PER) return oe_launch(decay_scan_kernel<PER, LL>, grid, block, 0, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d);
+    if (L == LL && per <= PER) return oe_launch(decay_scan_kernel<PER, LL>, grid, block, p.smem, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d, p.cols, p.chunk);
     OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
     OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
     OE_SCAN(8, 2) OE_SCAN(16, 2) OE_SCAN(32, 2) OE_SCAN(64, 2) OE_SCAN(128, 2)

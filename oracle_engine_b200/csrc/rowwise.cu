@@ -1,7 +1,8 @@
 // Row-wise kernels of layers that norm a sublayer's OUTPUT, gate heads, or rotate interleaved pairs:
 //
 //   cast_rows          y = x rounded to the compute type (a sublayer that reads the residual stream itself)
-//   rmsnorm_add        dst += coef * (y / sqrt(mean(y^2) + eps)) * w          (all float32)
+//   rmsnorm_add        dst (+)= coef * (y / sqrt(mean(y^2) + eps)) * w        (all float32), optionally with a
+//                      copy of the new dst rounded to bfloat16 (the next sublayer's input)
 //   relu2              a = max(a, 0)^2 in place
 //   tanh_rows          y = tanh(x), float32 in, compute type out
 //   head_gate          out[t, h, :] = [o / sqrt(mean(o^2) + eps)] * [w] * act(gate)   per head
@@ -23,19 +24,57 @@ __global__ void cast_rows_kernel(T* y, const float* x, size_t total) {
         y[i] = from_f32<T>(x[i]);
 }
 
-// One block per row.  The row is read twice (the second time from the L1/L2).
+// One block per row; up to 4,096 columns a thread keeps its part of the row in registers (float4 pieces).
+// accumulate == 0: dst is written, not read.  cast_out: null, or [rows, D] bfloat16 that receives the new dst.
 __global__ void __launch_bounds__(256)
-rmsnorm_add_kernel(float* dst, const float* y, const float* __restrict__ w, int D, float eps, float coef) {
+rmsnorm_add_kernel(float* dst, const float* y, const float* __restrict__ w, int D, float eps, float coef,
+                   int accumulate, bf16* cast_out) {
     __shared__ float red[32];
+    constexpr int KEEP = 4;
     pdl_launch_dependents();
     pdl_wait();
     const float* yr = y + (size_t)blockIdx.x * D;
     float* dr = dst + (size_t)blockIdx.x * D;
+    bf16* cr = cast_out ? cast_out + (size_t)blockIdx.x * D : nullptr;
+    const bool vec = (D % 4 == 0) && D <= KEEP * 4 * 256 && !(((uintptr_t)y | (uintptr_t)dst | (uintptr_t)w) & 15);
+    if (vec) {
+        const int n4 = D / 4;
+        float4 keep[KEEP];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {
+            const int i = threadIdx.x + j * 256;
+            keep[j] = i < n4 ? reinterpret_cast<const float4*>(yr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+        }
+        ss = block_sum(ss, red);
+        const float s = 1.f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < KEEP; j++) {
+            const int i = threadIdx.x + j * 256;
+            if (i < n4) {
+                const float4 g = reinterpret_cast<const float4*>(w)[i];
+                float4 d = accumulate ? reinterpret_cast<float4*>(dr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                d.x += coef * ((keep[j].x * s) * g.x); d.y += coef * ((keep[j].y * s) * g.y);
+                d.z += coef * ((keep[j].z * s) * g.z); d.w += coef * ((keep[j].w * s) * g.w);
+                reinterpret_cast<float4*>(dr)[i] = d;
+                if (cr) {
+                    cr[4 * i] = __float2bfloat16_rn(d.x); cr[4 * i + 1] = __float2bfloat16_rn(d.y);
+                    cr[4 * i + 2] = __float2bfloat16_rn(d.z); cr[4 * i + 3] = __float2bfloat16_rn(d.w);
+                }
+            }
+        }
+        return;
+    }
     float ss = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = yr[d]; ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
     const float s = 1.f / sqrtf(ss / (float)D + eps);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) dr[d] += coef * ((yr[d] * s) * w[d]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = (accumulate ? dr[d] : 0.f) + coef * ((yr[d] * s) * w[d]);
+        dr[d] = v;
+        if (cr) cr[d] = __float2bfloat16_rn(v);
+    }
 }
 
 template <typename T>
@@ -199,9 +238,10 @@ int oe_cast_rows_bf16(bf16* y, const float* x, long long total, cudaStream_t st)
     return oe_launch(cast_rows_kernel<bf16>, dim3(flat_blocks((size_t)total)), dim3(256), 0, st, y, x, (size_t)total);
 }
 
-int oe_rmsnorm_add(float* dst, const float* y, const float* w, int rows, int D, float eps, float coef, cudaStream_t st) {
+int oe_rmsnorm_add(float* dst, const float* y, const float* w, int rows, int D, float eps, float coef, int accumulate,
+                   bf16* cast_out, cudaStream_t st) {
     if (rows <= 0) return 0;
-    return oe_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), 0, st, dst, y, w, D, eps, coef);
+    return oe_launch(rmsnorm_add_kernel, dim3(rows), dim3(256), 0, st, dst, y, w, D, eps, coef, accumulate, cast_out);
 }
 
 int oe_relu2_f32(float* a, long long total, cudaStream_t st) {

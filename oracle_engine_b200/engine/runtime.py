@@ -35,6 +35,10 @@ class Runtime:
     # None).  The model and the block set it before they call a part; a part's last product may ask
     # the first megabytes of it into the L2 while its own epilogue runs (csrc/ops_tc.py: gemm(then=)).
     next_weights: torch.Tensor | None = None
+    # The float32 residual stream rounded to bfloat16, left by the kernel that last added into it (a norm's
+    # add_into(..., keep_cast=True)): (address of the stream, the copy).  `activations` takes it instead of casting
+    # again; the model clears it when a forward pass starts.
+    cast_cache: tuple | None = None
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
@@ -44,6 +48,9 @@ class Runtime:
         must not write to it), rounded to bfloat16 otherwise."""
         if self.dtype == torch.float32:
             return x
+        cached, self.cast_cache = self.cast_cache, None
+        if cached is not None and cached[0] == x.data_ptr() and cached[1].shape == x.shape:
+            return cached[1]
         from ..csrc import ops
         y = self.empty(*x.shape)
         ops.cast_rows(y, x)

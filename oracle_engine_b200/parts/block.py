@@ -61,13 +61,22 @@ class NormAfterBlock:
         rt = self.mixer.rt
         rt.next_weights = None
         y = rt.empty(*x.shape, dtype=x.dtype)
-        y.zero_()
-        self.mixer.forward(rt.activations(x), y, ctx, cache, state, owns_cache)
-        self.mixer_norm.add_into(x, y)
-        if self.feed_forward is not None:
+        h = rt.activations(x)
+        # a sublayer that can write its output (instead of adding it) saves the zeroing of the buffer
+        if getattr(self.mixer, "can_overwrite", False):
+            self.mixer.forward(h, y, ctx, cache, state, owns_cache, overwrite=True)
+        else:
             y.zero_()
-            self.feed_forward.forward(rt.activations(x), y, ctx)
-            self.ffn_norm.add_into(x, y)
+            self.mixer.forward(h, y, ctx, cache, state, owns_cache)
+        self.mixer_norm.add_into(x, y, keep_cast=True)
+        if self.feed_forward is not None:
+            h = rt.activations(x)
+            if getattr(self.feed_forward, "can_overwrite", False):
+                self.feed_forward.forward(h, y, ctx, overwrite=True)
+            else:
+                y.zero_()
+                self.feed_forward.forward(h, y, ctx)
+            self.ffn_norm.add_into(x, y, keep_cast=True)
 
 
 def _first_weights(part):

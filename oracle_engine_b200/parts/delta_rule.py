@@ -88,7 +88,10 @@ class GatedDelta(Part):
     def first_weights(self):
         return self.w_in
 
-    def forward(self, h, residual, ctx, cache, state, owns_cache=True):
+    can_overwrite = True
+
+    def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
         T, f32 = h.shape[0], torch.float32
         vv = self.H * self.dv
         proj = self.rt.empty(T, self.P, dtype=f32)
@@ -102,4 +105,4 @@ class GatedDelta(Part):
         ops.delta_rule_scan(o, state["S"], qkv, gb, ctx, self.G, self.H, self.dk, self.dv)
         y = self.rt.empty(T, vv)
         ops.head_gate(y, o, proj[:, self.C:self.C + vv], self.norm_w, self.H, self.dv, True, "silu", self.eps)
-        matmul_nt(self.rt, residual, y, self.w_o, accumulate=True)
+        matmul_nt(self.rt, residual, y, self.w_o, accumulate=not overwrite)

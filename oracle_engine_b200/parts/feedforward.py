@@ -94,8 +94,11 @@ class SquaredReLU(Part):
     def first_weights(self):
         return self.w_up
 
-    def forward(self, h, residual, ctx):
+    can_overwrite = True
+
+    def forward(self, h, residual, ctx, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
         a = self.rt.empty(h.shape[0], self.FF)
         matmul_nt(self.rt, a, h, self.w_up)
         ops.relu2_(a)
-        matmul_nt(self.rt, residual, a, self.w_down, accumulate=True)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=not overwrite)

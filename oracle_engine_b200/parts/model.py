@@ -122,6 +122,8 @@ class DecoderModel:
         return self.embedding.forward(ctx.token_ids, ctx.n_tokens, out)
 
     def run_entries(self, x, ctx, cache_views, state_views, lo: int, hi: int) -> None:
+        if lo == 0:
+            self.rt.cast_cache = None          # nothing of an earlier pass is taken for this one's stream
         for i in range(lo, hi):
             e = self.schedule[i]
             owner = i if e.cache_from is None else e.cache_from

@@ -36,6 +36,11 @@ class RMSNorm(Part):
         ops.rmsnorm(y, x, self.weight, self.eps)
         return y
 
-    def add_into(self, dst, y, coef: float = 1.0) -> None:
-        """dst += coef * norm(y); dst and y float32 of one shape."""
-        ops.rmsnorm_add(dst, y, self.weight, self.eps, coef)
+    def add_into(self, dst, y, coef: float = 1.0, accumulate: bool = True, keep_cast: bool = False) -> None:
+        """dst (+)= coef * norm(y); dst and y float32 of one shape.  keep_cast: on the bfloat16 path the kernel
+        also leaves the new dst rounded to bfloat16 for the sublayer that reads it next (Runtime.activations)."""
+        cast = None
+        if keep_cast and self.rt.dtype != dst.dtype:
+            cast = self.rt.empty(*dst.shape)
+            self.rt.cast_cache = (dst.data_ptr(), cast)
+        ops.rmsnorm_add(dst, y, self.weight, self.eps, coef, accumulate, cast)

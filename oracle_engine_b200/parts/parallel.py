@@ -72,11 +72,17 @@ class ParallelMixers(Part):
         f = getattr(self.branches[0][1], "first_weights", None)
         return f() if f is not None else None
 
-    def forward(self, h, residual, ctx, cache, state, owns_cache=True):
+    can_overwrite = True
+
+    def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
         coef = 1.0 / len(self.branches)
         y = self.rt.empty(h.shape[0], self.D, dtype=torch.float32)
-        for tag, m, _ in self.branches:
-            y.zero_()
+        for i, (tag, m, _) in enumerate(self.branches):
             own = {name[len(tag) + 1:]: t for name, t in state.items() if name.startswith(tag + ".")}
-            m.forward(h, y, ctx, cache, own, owns_cache)
-            ops.rmsnorm_add(residual, y, self.out_w[tag], self.eps, coef)
+            if getattr(m, "can_overwrite", False):
+                m.forward(h, y, ctx, cache, own, owns_cache, overwrite=True)
+            else:
+                y.zero_()
+                m.forward(h, y, ctx, cache, own, owns_cache)
+            ops.rmsnorm_add(residual, y, self.out_w[tag], self.eps, coef, accumulate=not (overwrite and i == 0))

@@ -85,7 +85,10 @@ class SinkAttention(Part):
     def first_weights(self):
         return self.w_in
 
-    def forward(self, h, residual, ctx, cache, state, owns_cache=True):
+    can_overwrite = True
+
+    def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
         T = h.shape[0]
         qw, kw = self.H * self.hd, self.G * self.hd
         width = qw + kw + (qw if self.gate else 0)
@@ -103,4 +106,4 @@ class SinkAttention(Part):
             y = self.rt.empty(T, qw)
             ops.head_gate(y, o, qkg[:, qw + kw:], None, self.H, self.hd, False, "sigmoid")
             o = y
-        matmul_nt(self.rt, residual, o, self.w_o, accumulate=True)
+        matmul_nt(self.rt, residual, o, self.w_o, accumulate=not overwrite)

@@ -77,7 +77,10 @@ class DecayTimeMix(Part):
     def first_weights(self):
         return self.w.get("r")
 
-    def forward(self, h, residual, ctx, cache, state, owns_cache=True):
+    can_overwrite = True
+
+    def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
         T, f32, hd = h.shape[0], torch.float32, self.H * self.d
         mix = self.rt.empty(len(_MIXES), T, self.D)
         ops.token_shift_mix(mix, h, self.mu, state["prev"], ctx)
@@ -94,4 +97,4 @@ class DecayTimeMix(Part):
         ops.decay_scan(o, state["S"], r, k, v, z, self.u, self.w0, ctx, self.H, self.d)
         y = self.rt.empty(T, hd)
         ops.head_gate(y, o, g, self.norm_w, self.H, self.d, True, "silu", self.eps)
-        matmul_nt(self.rt, residual, y, self.w["o"], accumulate=True)
+        matmul_nt(self.rt, residual, y, self.w["o"], accumulate=not overwrite)
