@@ -26,6 +26,9 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
@@ -165,8 +168,25 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
 #pragma unroll
     for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)lane_row<L>(i, l) * dv + j] : 0.f;
 
+    // 16-byte copies where every piece starts on a 16-byte boundary, else 4-byte copies
+    const bool vec = ((dk | cols | dv | C) & 3) == 0 && (((uintptr_t)qkv) & 15) == 0;
     auto issue = [&](int c0, float* dst) {
         const int cn = min(chunk, n - c0);
+        if (vec) {
+            const int kq4 = dk / 2, v4 = cols / 4, vpt = kq4 + v4;        // 16-byte pieces of a token: k and q, v columns
+            for (int e = threadIdx.x; e < cn * vpt; e += blockDim.x) {
+                const int tt = e / vpt, r = e % vpt;
+                const float* rowp = qkv + (size_t)(row0 + c0 + tt) * C;
+                float* d = dst + tt * tokf;
+                if (r < dk / 4) cp_async16(d + 4 * r, rowp + (size_t)(G + g) * dk + 4 * r);
+                else if (r < kq4) cp_async16(d + 4 * r, rowp + (size_t)g * dk + 4 * (r - dk / 4));
+                else if (col0 + 4 * (r - kq4) < dv) cp_async16(d + 2 * dk + 4 * (r - kq4), rowp + (size_t)2 * G * dk + (size_t)h * dv + col0 + 4 * (r - kq4));
+            }
+            for (int e = threadIdx.x; e < cn * 2; e += blockDim.x)
+                cp_async4(dst + (e >> 1) * tokf + 2 * dk + cols + (e & 1), gb + (size_t)(row0 + c0 + (e >> 1)) * 2 * H + (size_t)(e & 1) * H + h);
+            cp_async_commit();
+            return;
+        }
         for (int e = threadIdx.x; e < cn * tokf; e += blockDim.x) {
             const int tt = e / tokf, r = e % tokf;
             const size_t row = (size_t)(row0 + c0 + tt);
@@ -188,6 +208,10 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
         else cp_async_wait<0>();
         __syncthreads();
         const float* base = stage_mem + buf * stagef;
+        // The read-out o = S^T q of a token does not feed the next token's update, so its sum over the lanes
+        // and its store are issued behind the next token's products with k (pend: the token it belongs to).
+        float pend_acc = 0.f;
+        long long pend = -1;
         for (int tt = 0; tt < cn; tt++) {
             const float* tk = base + tt * tokf;
             const float decay = tk[2 * dk + cols], beta = tk[2 * dk + cols + 1];
@@ -208,6 +232,10 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
                         d2 = fmaf(kv.z, s[i + 2], d2); d3 = fmaf(kv.w, s[i + 3], d3);
                     }
                 }
+            }
+            if (pend >= 0) {
+                const float acc = lanes_sum<L>(pend_acc);
+                if (mine && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
             }
             const float dot = lanes_sum<L>((d0 + d1) + (d2 + d3));
             const float u = beta * (v - dot);
@@ -230,8 +258,12 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
                     }
                 }
             }
-            const float acc = lanes_sum<L>((a0 + a1) + (a2 + a3));
-            if (mine && l == 0) o[(size_t)(row0 + c0 + tt) * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
+            pend_acc = (a0 + a1) + (a2 + a3);
+            pend = (long long)(row0 + c0 + tt);
+        }
+        if (pend >= 0) {
+            const float acc = lanes_sum<L>(pend_acc);
+            if (mine && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
         }
         __syncthreads();
     }
@@ -304,8 +336,24 @@ decay_scan_kernel(float* o, float* state, const float* r, const float* k, const 
 #pragma unroll
     for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)lane_row<L>(i, l) * d + j] : 0.f;
 
+    const bool vec = ((d | cols) & 3) == 0 && (stride & 3) == 0 &&
+                     ((((uintptr_t)r) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)z)) & 15) == 0;
     auto issue = [&](int c0, float* dst) {
         const int cn = min(chunk, n - c0);
+        if (vec) {
+            const int d4 = d / 4, v4 = cols / 4, vpt = 3 * d4 + v4;      // 16-byte pieces of a token: r, k, z, v columns
+            for (int e = threadIdx.x; e < cn * vpt; e += blockDim.x) {
+                const int tt = e / vpt, q = e % vpt;
+                const size_t at = (size_t)(row0 + c0 + tt) * stride + (size_t)h * d;
+                float* dd = dst + tt * tokf;
+                if (q < d4) cp_async16(dd + 4 * q, r + at + 4 * q);
+                else if (q < 2 * d4) cp_async16(dd + dp + 4 * (q - d4), k + at + 4 * (q - d4));
+                else if (q < 3 * d4) cp_async16(dd + 2 * dp + 4 * (q - 2 * d4), z + at + 4 * (q - 2 * d4));
+                else if (col0 + 4 * (q - 3 * d4) < d) cp_async16(dd + 4 * dp + 4 * (q - 3 * d4), v + at + col0 + 4 * (q - 3 * d4));
+            }
+            cp_async_commit();
+            return;
+        }
         for (int e = threadIdx.x; e < cn * tokf; e += blockDim.x) {
             const int tt = e / tokf, q = e % tokf, which = q / dp, i = q % dp;
             const size_t at = (size_t)(row0 + c0 + tt) * stride + (size_t)h * d;
