@@ -216,29 +216,45 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
             const float* tk = base + tt * tokf;
             const float decay = tk[2 * dk + cols], beta = tk[2 * dk + cols + 1];
             const float v = tk[2 * dk + (jj < cols ? jj : 0)];
+            // k . (g S) = g (k . S): the products with k use the state as the last token left it, and the
+            // state is scaled while their sum travels between the lanes
             float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
             if (L == 1) {
 #pragma unroll
                 for (int i = 0; i < PER; i++)
-                    if (i < per) { s[i] *= decay; d0 = fmaf(tk[i], s[i], d0); }
+                    if (i < per) d0 = fmaf(tk[i], s[i], d0);
             } else {
                 const float4* k4 = reinterpret_cast<const float4*>(tk);
 #pragma unroll
                 for (int i = 0; i < PER; i += 4) {
                     if (i < per) {
                         const float4 kv = k4[(i >> 2) * L + l];
-                        s[i] *= decay; s[i + 1] *= decay; s[i + 2] *= decay; s[i + 3] *= decay;
                         d0 = fmaf(kv.x, s[i], d0); d1 = fmaf(kv.y, s[i + 1], d1);
                         d2 = fmaf(kv.z, s[i + 2], d2); d3 = fmaf(kv.w, s[i + 3], d3);
                     }
                 }
             }
+            float dsum = (d0 + d1) + (d2 + d3);
+#pragma unroll
+            for (int sh = 1; sh < L; sh <<= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, dsum, sh);
+                if (sh == 1) {
+#pragma unroll
+                    for (int i = 0; i < PER; i++)
+                        if (i < per) s[i] *= decay;
+                }
+                dsum += other;
+            }
+            if (L == 1) {
+#pragma unroll
+                for (int i = 0; i < PER; i++)
+                    if (i < per) s[i] *= decay;
+            }
             if (pend >= 0) {
                 const float acc = lanes_sum<L>(pend_acc);
                 if (mine && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
             }
-            const float dot = lanes_sum<L>((d0 + d1) + (d2 + d3));
-            const float u = beta * (v - dot);
+            const float u = beta * (v - decay * dsum);
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
             if (L == 1) {
 #pragma unroll
@@ -422,8 +438,11 @@ decay_scan_kernel(float* o, float* state, const float* r, const float* k, const 
 }
 
 // How a scan is laid out: lanes per column (the most of 8, 4, 2 that leave each lane a multiple of four rows
-// and at least eight, else 1), columns per block (32, or all where a lane keeps 64 rows or more), tokens per
-// staged chunk (the most of 16, 8, 4, 2, 1 whose two stages fit 48 KB).
+// and at least eight, else 1), columns per block (up to 32), tokens per staged chunk (the most of 16, 8, 4, 2, 1
+// whose two stages fit 48 KB).  Measured on a B200, one sequence of 2,048 tokens, 16 heads of 128 x 128
+// (us; lanes x columns): 8 x 32 1,116, 8 x 16 1,138, 4 x 32 2,088, 2 x 32 2,586; 16 lanes: 833 but a decode
+// step of 64 sequences 87 instead of 53 (a lane's share of a column's rows is what the time follows: the
+// kernel issues about 190 instructions a token and warp, with one or two warps a scheduler).
 struct ScanPlan { int L, cols, threads, chunk; size_t smem; };
 inline ScanPlan scan_plan(int rows, int ncols, int tok_floats_without_cols, int pad_cols) {
     ScanPlan p;
@@ -467,7 +486,7 @@ int oe_conv_state_update(float* conv_state, const float* proj, int P, int C, int
 int oe_delta_rule_scan(float* o, float* state, const float* qkv, const float* gb, const int* seq_slot, const int* cu_q,
                        int n_seqs, int G, int H, int dk, int dv, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
-    if (dk < 1 || dk > 256 || dv < 1 || dv > 256 || G < 1 || H % G || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
+    if (dk < 1 || dk > 256 || dv < 1 || dv > 4096 || G < 1 || H % G || n_seqs > 65535) return OE_ERR_UNSUPPORTED;
     const ScanPlan p = scan_plan(dk, dv, 2 * dk + 2, 0);
     if (p.cols < 1 || p.smem > 48 * 1024) return OE_ERR_UNSUPPORTED;
     const int L = p.L, per = dk / L;

@@ -25,6 +25,10 @@ from pathlib import Path
 import numpy as np
 
 
+SLACK_REQUESTS = 64       # live requests whose last, partly filled page the cache has room for beyond --max-tokens
+MAX_SLOTS = 1024          # the most requests a replay holds at once
+
+
 def replay(engine, lines, out_dir: Path, log=sys.stdout) -> int:
     from .batch import SequenceStep
 
@@ -71,9 +75,14 @@ def main(argv=None) -> int:
     ap.add_argument("--no-graphs", action="store_true", help="do not capture CUDA graphs for one-token steps")
     args = ap.parse_args(argv)
 
+    from ..csrc.ops import PAGE
     from .engine import Engine
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
-                                    use_graphs=not args.no_graphs)
+    # The cache holds whole pages: every live request may leave most of its last page unused, so room for
+    # SLACK_REQUESTS such pages is added to what the trace says its requests hold.  A model with recurrent
+    # layers keeps a state per slot, so the slots are bounded too.
+    tokens = int(args.max_tokens) + SLACK_REQUESTS * PAGE
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=tokens, max_seq_len=tokens,
+                                    n_slots=min(MAX_SLOTS, max(1, tokens // PAGE)), use_graphs=not args.no_graphs)
     replay(engine, sys.stdin, Path(args.out))
     return 0
 

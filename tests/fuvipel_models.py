@@ -37,6 +37,12 @@ F2 = config(257, 120, 3e-6, [
 F3 = config(131, 100, 1e-6, [
     delta(5, 5, 20, 12, 1, ff=72),
     parallel(5, 1, 20, 0.25, {"dims": 4, "base": 77.0}, 2, 50, 6, ff=40)])
+# sizes that are no multiples of four (scalar staging in the scans, one lane per state column), an attention
+# head size the tensor-core kernels do not take, six taps, a value size above the key size
+F4 = config(97, 72, 2e-5, [
+    delta(3, 1, 15, 10, 6),
+    parallel(2, 1, 34, 0.2, {"dims": 10, "base": 1000.0}, 3, 30, 5, ff=50),
+    delta(2, 2, 8, 70, 2, ff=36)])
 # peaked attention: one key decides a query's output, so a key that is lost or wrong shows
 SHARP = config(200, 64, 1e-5, [
     parallel(4, 2, 32, 1.0, {"dims": 32, "base": 10000.0}, 2, 32, 8),
@@ -48,7 +54,7 @@ REAL = config(1000, 1024, 1e-6, [
     delta(8, 4, 128, 128, 4),
     parallel(6, 6, 64, 0.125, {"dims": 64, "base": 10000.0}, 4, 128, 16)])
 
-ALL = {"F1": (F1, 3), "F2": (F2, 4), "F3": (F3, 5), "SHARP": (SHARP, 6)}
+ALL = {"F1": (F1, 3), "F2": (F2, 4), "F3": (F3, 5), "F4": (F4, 7), "SHARP": (SHARP, 6)}
 
 
 def write(folder, raw, seed, std=0.1, long_memory=True):

@@ -47,7 +47,7 @@ def _compare(got, plain, requests, tol, what, cache={}):
                                 f"{int((err >= tol).argmax())}, worst {int(err.argmax())}: {err.max()}"
 
 
-@pytest.mark.parametrize("name", ["F1", "F2", "F3"])
+@pytest.mark.parametrize("name", ["F1", "F2", "F3", "F4"])
 def test_every_layer_by_itself_float32(models, name):
     """The residual stream after each layer of a whole prompt, in float32, against the plain model."""
     from oracle_engine_b200 import SequenceStep
@@ -93,7 +93,7 @@ def test_each_branch_of_a_parallel_layer_alone(tmp_path, branch):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["F1", "F2", "F3"])
+@pytest.mark.parametrize("name", ["F1", "F2", "F3", "F4"])
 def test_whole_decoded_pieces_and_batches_agree_with_plain(models, tmp_path, name, dtype):
     folder, plain = models[name]
     vocab = plain.cfg["vocab"]
