@@ -7,7 +7,7 @@ are float32 in both.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -39,9 +39,33 @@ class Runtime:
     # add_into(..., keep_cast=True)): (address of the stream, the copy).  `activations` takes it instead of casting
     # again; the model clears it when a forward pass starts.
     cast_cache: tuple | None = None
+    _buffers: dict = field(default_factory=dict, repr=False)
+    _cast_turn: int = 0
 
     def empty(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def buffer(self, tag: str, *shape, dtype=None) -> torch.Tensor:
+        """A tensor for an intermediate result of a step, kept under `tag` and handed out again at the next
+        request for that tag (whatever the shape: the storage grows to the largest one asked for).  A prompt
+        step of thousands of tokens asks for dozens of buffers of tens of megabytes in every layer; kept
+        buffers take those requests away from the caching allocator.  Two results that are alive at the same time
+        need different tags; everything runs on one stream, so a buffer's next user writes after its last
+        reader has run.  While a CUDA graph is being captured this is `empty` (the graph owns its memory)."""
+        dtype = dtype or self.dtype
+        if self.device.type != "cuda" or torch.cuda.is_current_stream_capturing():
+            return self.empty(*shape, dtype=dtype)
+        n = 1
+        for d in shape:
+            n *= int(d)
+        key = (tag, dtype)
+        flat = self._buffers.get(key)
+        if flat is None or flat.numel() < n:
+            flat = None
+            self._buffers.pop(key, None)
+            flat = torch.empty(max(n + n // 4, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = flat
+        return flat[:n].view(*shape)
 
     def activations(self, x: torch.Tensor) -> torch.Tensor:
         """The float32 residual stream as a sublayer's input: itself on the 32-bit path (the sublayer
@@ -52,7 +76,7 @@ class Runtime:
         if cached is not None and cached[0] == x.data_ptr() and cached[1].shape == x.shape:
             return cached[1]
         from ..csrc import ops
-        y = self.empty(*x.shape)
+        y = self.buffer("activations", *x.shape)
         ops.cast_rows(y, x)
         return y
 

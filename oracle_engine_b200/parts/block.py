@@ -60,7 +60,7 @@ class NormAfterBlock:
     def forward(self, x, ctx, cache, state, owns_cache=True):
         rt = self.mixer.rt
         rt.next_weights = None
-        y = rt.empty(*x.shape, dtype=x.dtype)
+        y = rt.buffer("sublayer_out", *x.shape, dtype=x.dtype)
         h = rt.activations(x)
         # a sublayer that can write its output (instead of adding it) saves the zeroing of the buffer
         if getattr(self.mixer, "can_overwrite", False):

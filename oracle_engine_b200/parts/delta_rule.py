@@ -94,15 +94,16 @@ class GatedDelta(Part):
         """overwrite: the output is written into `residual` (float32) instead of added."""
         T, f32 = h.shape[0], torch.float32
         vv = self.H * self.dv
-        proj = self.rt.empty(T, self.P, dtype=f32)
+        buf = self.rt.buffer
+        proj = buf("delta.proj", T, self.P, dtype=f32)
         matmul_nt(self.rt, proj, h, self.w_in)
-        qkv = self.rt.empty(T, self.C, dtype=f32)
-        gb = self.rt.empty(T, 2 * self.H, dtype=f32)
+        qkv = buf("delta.qkv", T, self.C, dtype=f32)
+        gb = buf("delta.gb", T, 2 * self.H, dtype=f32)
         ops.short_conv_prepare(qkv, gb, proj, self.conv_w, state["conv"], self.A_log, self.dt_bias, ctx, self.G,
                                self.H, self.dk, self.dv, self.dk ** -0.5)
         ops.conv_state_update(state["conv"], proj, self.C, self.taps, ctx)
-        o = self.rt.empty(T, vv, dtype=f32)
+        o = buf("delta.o", T, vv, dtype=f32)
         ops.delta_rule_scan(o, state["S"], qkv, gb, ctx, self.G, self.H, self.dk, self.dv)
-        y = self.rt.empty(T, vv)
+        y = buf("delta.y", T, vv)
         ops.head_gate(y, o, proj[:, self.C:self.C + vv], self.norm_w, self.H, self.dv, True, "silu", self.eps)
         matmul_nt(self.rt, residual, y, self.w_o, accumulate=not overwrite)

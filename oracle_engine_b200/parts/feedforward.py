@@ -98,7 +98,7 @@ class SquaredReLU(Part):
 
     def forward(self, h, residual, ctx, overwrite: bool = False):
         """overwrite: the output is written into `residual` (float32) instead of added."""
-        a = self.rt.empty(h.shape[0], self.FF)
+        a = self.rt.buffer("relu2.a", h.shape[0], self.FF)
         matmul_nt(self.rt, a, h, self.w_up)
         ops.relu2_(a)
         matmul_nt(self.rt, residual, a, self.w_down, accumulate=not overwrite)

@@ -41,6 +41,8 @@ class RMSNorm(Part):
         also leaves the new dst rounded to bfloat16 for the sublayer that reads it next (Runtime.activations)."""
         cast = None
         if keep_cast and self.rt.dtype != dst.dtype:
-            cast = self.rt.empty(*dst.shape)
+            # two buffers in turn: the copy a sublayer is reading stays while the next one is written
+            self.rt._cast_turn ^= 1
+            cast = self.rt.buffer(f"stream_copy{self.rt._cast_turn}", *dst.shape)
             self.rt.cast_cache = (dst.data_ptr(), cast)
         ops.rmsnorm_add(dst, y, self.weight, self.eps, coef, accumulate, cast)

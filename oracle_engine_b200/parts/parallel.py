@@ -77,7 +77,7 @@ class ParallelMixers(Part):
     def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
         """overwrite: the output is written into `residual` (float32) instead of added."""
         coef = 1.0 / len(self.branches)
-        y = self.rt.empty(h.shape[0], self.D, dtype=torch.float32)
+        y = self.rt.buffer("parallel.branch_out", h.shape[0], self.D, dtype=torch.float32)
         for i, (tag, m, _) in enumerate(self.branches):
             own = {name[len(tag) + 1:]: t for name, t in state.items() if name.startswith(tag + ".")}
             if getattr(m, "can_overwrite", False):

@@ -94,16 +94,16 @@ class SinkAttention(Part):
         width = qw + kw + (qw if self.gate else 0)
         if not owns_cache:
             raise ValueError("sink_attention: reading another entry's cache is not supported")
-        qkg = self.rt.empty(T, width)
+        qkg = self.rt.buffer("sink.qkg", T, width)
         matmul_nt(self.rt, qkg, h, self.w_in)
         inv_freq, dims = self.position.tables() if self.position is not None else (None, 0)
         ops.rot_norm_kv_write(qkg, inv_freq, dims, cache.kv, cache.tables, ctx.tok_seq, ctx.tok_pos, self.H, self.G,
                               self.hd, self.eps, True)
-        o = self.rt.empty(T, qw)
+        o = self.rt.buffer("sink.o", T, qw)
         from . import attention_dispatch as ad
         ad.attend(self.rt, o, qkg, cache, ctx, self.H, self.G, self.hd, self.window, self.scale, sink=True)
         if self.gate:
-            y = self.rt.empty(T, qw)
+            y = self.rt.buffer("sink.y", T, qw)
             ops.head_gate(y, o, qkg[:, qw + kw:], None, self.H, self.hd, False, "sigmoid")
             o = y
         matmul_nt(self.rt, residual, o, self.w_o, accumulate=not overwrite)

@@ -82,19 +82,20 @@ class DecayTimeMix(Part):
     def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
         """overwrite: the output is written into `residual` (float32) instead of added."""
         T, f32, hd = h.shape[0], torch.float32, self.H * self.d
-        mix = self.rt.empty(len(_MIXES), T, self.D)
+        buf = self.rt.buffer
+        mix = buf("mix.in", len(_MIXES), T, self.D)
         ops.token_shift_mix(mix, h, self.mu, state["prev"], ctx)
         ops.last_rows_to_state(state["prev"], h, ctx)
-        r, k, v, g, z = (self.rt.empty(T, hd, dtype=f32) for _ in range(5))
+        r, k, v, g, z = (buf("mix." + n, T, hd, dtype=f32) for n in "rkvgz")
         for out, i, name in ((r, 0, "r"), (k, 1, "k"), (v, 2, "v"), (g, 3, "g")):
             matmul_nt(self.rt, out, mix[i], self.w[name])
-        low = self.rt.empty(T, self.rank, dtype=f32)
+        low = buf("mix.low", T, self.rank, dtype=f32)
         matmul_nt(self.rt, low, mix[4], self.w["w1"])
-        th = self.rt.empty(T, self.rank)
+        th = buf("mix.tanh", T, self.rank)
         ops.tanh_rows(th, low)
         matmul_nt(self.rt, z, th, self.w["w2"])
-        o = self.rt.empty(T, hd, dtype=f32)
+        o = buf("mix.o", T, hd, dtype=f32)
         ops.decay_scan(o, state["S"], r, k, v, z, self.u, self.w0, ctx, self.H, self.d)
-        y = self.rt.empty(T, hd)
+        y = buf("mix.y", T, hd)
         ops.head_gate(y, o, g, self.norm_w, self.H, self.d, True, "silu", self.eps)
         matmul_nt(self.rt, residual, y, self.w["o"], accumulate=not overwrite)
