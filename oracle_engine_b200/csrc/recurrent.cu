@@ -144,7 +144,7 @@ __device__ __forceinline__ int lane_row(int ii, int l) { return L == 1 ? ii : ((
 // tokens are walked in order in chunks: while one chunk is computed, the next chunk's k, q (dk each), the
 // block's v columns, the decay and the step size arrive in shared memory by asynchronous copies.
 // qkv row [q: G*dk | k: G*dk | v: H*dv], gb row [g: H | beta: H]; o [T, H*dv] float32.
-template <int PER, int L>
+template <int PER, int L, int NC>
 __global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb,
                        const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
@@ -154,19 +154,24 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
     pdl_wait();
     const int tiles = (dv + cols - 1) / cols;
     const int h = blockIdx.x / tiles, col0 = (blockIdx.x % tiles) * cols, b = blockIdx.y;
-    const int jj = threadIdx.x / L, l = threadIdx.x % L, j = col0 + jj;
+    // a thread keeps its rows of NC adjacent columns: what it reads of k and q serves all of them
+    const int jj = (threadIdx.x / L) * NC, l = threadIdx.x % L, j = col0 + jj;
     const int slot = seq_slot[b];
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
     const int g = h / (H / G);
     const int C = 2 * G * dk + H * dv;
     const int per = dk / L;
-    const bool mine = jj < cols && j < dv;
+    bool mine[NC];
+#pragma unroll
+    for (int c = 0; c < NC; c++) mine[c] = jj + c < cols && j + c < dv;
     const int tokf = (2 * dk + cols + 2 + 3) / 4 * 4;            // floats of a staged token: k, q, v columns, g, beta
     float* S = state + (((size_t)slot * H + h) * dk) * dv;
-    float s[PER];
+    float s[NC][PER];
 #pragma unroll
-    for (int i = 0; i < PER; i++) s[i] = (mine && i < per) ? S[(size_t)lane_row<L>(i, l) * dv + j] : 0.f;
+    for (int c = 0; c < NC; c++)
+#pragma unroll
+        for (int i = 0; i < PER; i++) s[c][i] = (mine[c] && i < per) ? S[(size_t)lane_row<L>(i, l) * dv + j + c] : 0.f;
 
     // 16-byte copies where every piece starts on a 16-byte boundary, else 4-byte copies
     const bool vec = ((dk | cols | dv | C) & 3) == 0 && (((uintptr_t)qkv) & 15) == 0;
@@ -210,56 +215,89 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
         const float* base = stage_mem + buf * stagef;
         // The read-out o = S^T q of a token does not feed the next token's update, so its sum over the lanes
         // and its store are issued behind the next token's products with k (pend: the token it belongs to).
-        float pend_acc = 0.f;
+        float pend_acc[NC];
+#pragma unroll
+        for (int c = 0; c < NC; c++) pend_acc[c] = 0.f;
         long long pend = -1;
         for (int tt = 0; tt < cn; tt++) {
             const float* tk = base + tt * tokf;
             const float decay = tk[2 * dk + cols], beta = tk[2 * dk + cols + 1];
-            const float v = tk[2 * dk + (jj < cols ? jj : 0)];
+            float v[NC], d[NC][4];
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                v[c] = tk[2 * dk + (jj + c < cols ? jj + c : 0)];
+                d[c][0] = d[c][1] = d[c][2] = d[c][3] = 0.f;
+            }
             // k . (g S) = g (k . S): the products with k use the state as the last token left it, and the
             // state is scaled while their sum travels between the lanes
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
             if (L == 1) {
 #pragma unroll
                 for (int i = 0; i < PER; i++)
-                    if (i < per) d0 = fmaf(tk[i], s[i], d0);
+                    if (i < per) {
+                        const float kv = tk[i];
+#pragma unroll
+                        for (int c = 0; c < NC; c++) d[c][0] = fmaf(kv, s[c][i], d[c][0]);
+                    }
             } else {
                 const float4* k4 = reinterpret_cast<const float4*>(tk);
 #pragma unroll
                 for (int i = 0; i < PER; i += 4) {
                     if (i < per) {
                         const float4 kv = k4[(i >> 2) * L + l];
-                        d0 = fmaf(kv.x, s[i], d0); d1 = fmaf(kv.y, s[i + 1], d1);
-                        d2 = fmaf(kv.z, s[i + 2], d2); d3 = fmaf(kv.w, s[i + 3], d3);
+#pragma unroll
+                        for (int c = 0; c < NC; c++) {
+                            d[c][0] = fmaf(kv.x, s[c][i], d[c][0]); d[c][1] = fmaf(kv.y, s[c][i + 1], d[c][1]);
+                            d[c][2] = fmaf(kv.z, s[c][i + 2], d[c][2]); d[c][3] = fmaf(kv.w, s[c][i + 3], d[c][3]);
+                        }
                     }
                 }
             }
-            float dsum = (d0 + d1) + (d2 + d3);
+            float dsum[NC];
+#pragma unroll
+            for (int c = 0; c < NC; c++) dsum[c] = (d[c][0] + d[c][1]) + (d[c][2] + d[c][3]);
 #pragma unroll
             for (int sh = 1; sh < L; sh <<= 1) {
-                const float other = __shfl_xor_sync(0xffffffffu, dsum, sh);
+                float other[NC];
+#pragma unroll
+                for (int c = 0; c < NC; c++) other[c] = __shfl_xor_sync(0xffffffffu, dsum[c], sh);
                 if (sh == 1) {
 #pragma unroll
-                    for (int i = 0; i < PER; i++)
-                        if (i < per) s[i] *= decay;
+                    for (int c = 0; c < NC; c++)
+#pragma unroll
+                        for (int i = 0; i < PER; i++)
+                            if (i < per) s[c][i] *= decay;
                 }
-                dsum += other;
+#pragma unroll
+                for (int c = 0; c < NC; c++) dsum[c] += other[c];
             }
             if (L == 1) {
 #pragma unroll
-                for (int i = 0; i < PER; i++)
-                    if (i < per) s[i] *= decay;
+                for (int c = 0; c < NC; c++)
+#pragma unroll
+                    for (int i = 0; i < PER; i++)
+                        if (i < per) s[c][i] *= decay;
             }
             if (pend >= 0) {
-                const float acc = lanes_sum<L>(pend_acc);
-                if (mine && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
+#pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    const float acc = lanes_sum<L>(pend_acc[c]);
+                    if (mine[c] && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j + c] = acc;
+                }
             }
-            const float u = beta * (v - decay * dsum);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float u[NC], a[NC][4];
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                u[c] = beta * (v[c] - decay * dsum[c]);
+                a[c][0] = a[c][1] = a[c][2] = a[c][3] = 0.f;
+            }
             if (L == 1) {
 #pragma unroll
                 for (int i = 0; i < PER; i++)
-                    if (i < per) { s[i] = fmaf(tk[i], u, s[i]); a0 = fmaf(tk[dk + i], s[i], a0); }
+                    if (i < per) {
+                        const float kv = tk[i], qv = tk[dk + i];
+#pragma unroll
+                        for (int c = 0; c < NC; c++) { s[c][i] = fmaf(kv, u[c], s[c][i]); a[c][0] = fmaf(qv, s[c][i], a[c][0]); }
+                    }
             } else {
                 const float4* k4 = reinterpret_cast<const float4*>(tk);
                 const float4* q4 = reinterpret_cast<const float4*>(tk + dk);
@@ -267,26 +305,36 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
                 for (int i = 0; i < PER; i += 4) {
                     if (i < per) {
                         const float4 kv = k4[(i >> 2) * L + l], qv = q4[(i >> 2) * L + l];
-                        s[i] = fmaf(kv.x, u, s[i]); s[i + 1] = fmaf(kv.y, u, s[i + 1]);
-                        s[i + 2] = fmaf(kv.z, u, s[i + 2]); s[i + 3] = fmaf(kv.w, u, s[i + 3]);
-                        a0 = fmaf(qv.x, s[i], a0); a1 = fmaf(qv.y, s[i + 1], a1);
-                        a2 = fmaf(qv.z, s[i + 2], a2); a3 = fmaf(qv.w, s[i + 3], a3);
+#pragma unroll
+                        for (int c = 0; c < NC; c++) {
+                            s[c][i] = fmaf(kv.x, u[c], s[c][i]); s[c][i + 1] = fmaf(kv.y, u[c], s[c][i + 1]);
+                            s[c][i + 2] = fmaf(kv.z, u[c], s[c][i + 2]); s[c][i + 3] = fmaf(kv.w, u[c], s[c][i + 3]);
+                            a[c][0] = fmaf(qv.x, s[c][i], a[c][0]); a[c][1] = fmaf(qv.y, s[c][i + 1], a[c][1]);
+                            a[c][2] = fmaf(qv.z, s[c][i + 2], a[c][2]); a[c][3] = fmaf(qv.w, s[c][i + 3], a[c][3]);
+                        }
                     }
                 }
             }
-            pend_acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+            for (int c = 0; c < NC; c++) pend_acc[c] = (a[c][0] + a[c][1]) + (a[c][2] + a[c][3]);
             pend = (long long)(row0 + c0 + tt);
         }
         if (pend >= 0) {
-            const float acc = lanes_sum<L>(pend_acc);
-            if (mine && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j] = acc;
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                const float acc = lanes_sum<L>(pend_acc[c]);
+                if (mine[c] && l == 0) o[(size_t)pend * (size_t)(H * dv) + (size_t)h * dv + j + c] = acc;
+            }
         }
         __syncthreads();
     }
-    if (mine) {
 #pragma unroll
-        for (int i = 0; i < PER; i++)
-            if (i < per) S[(size_t)lane_row<L>(i, l) * dv + j] = s[i];
+    for (int c = 0; c < NC; c++) {
+        if (mine[c]) {
+#pragma unroll
+            for (int i = 0; i < PER; i++)
+                if (i < per) S[(size_t)lane_row<L>(i, l) * dv + j + c] = s[c][i];
+        }
     }
 }
 
@@ -490,9 +538,16 @@ int oe_delta_rule_scan(float* o, float* state, const float* qkv, const float* gb
     const ScanPlan p = scan_plan(dk, dv, 2 * dk + 2, 0);
     if (p.cols < 1 || p.smem > 48 * 1024) return OE_ERR_UNSUPPORTED;
     const int L = p.L, per = dk / L;
-    const dim3 grid(H * ((dv + p.cols - 1) / p.cols), n_seqs), block(p.threads);
+    // Two columns a thread where a lane keeps at most 16 rows of each (registers) and the columns pair up: what a
+    // thread reads of k and q then serves both (16 heads of 128 x 128, us, one / two columns: 8 sequences of 512
+    // tokens 733 / 449, 64 sequences of one token 52 / 46, one sequence of 2,048 tokens 1,364 / 1,102).
+    const int nc = (per <= 16 && p.cols % 2 == 0 && L > 1) ? 2 : 1;
+    const dim3 grid(H * ((dv + p.cols - 1) / p.cols), n_seqs), block(((p.cols / nc) * L + 31) / 32 * 32);
 #define OE_SCAN(PER, LL) \
-    if (L == LL && per <= PER) return oe_launch(delta_rule_scan_kernel<PER, LL>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk);
+    if (L == LL && per <= PER) { \
+        if (nc == 2 && PER <= 16) return oe_launch(delta_rule_scan_kernel<(PER <= 16 ? PER : 16), LL, 2>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
+        return oe_launch(delta_rule_scan_kernel<PER, LL, 1>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
+    }
     OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
     OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
     OE_SCAN(8, 2) OE_SCAN(16, 2) OE_SCAN(32, 2) OE_SCAN(64, 2) OE_SCAN(128, 2)
