@@ -144,7 +144,7 @@ __device__ __forceinline__ int lane_row(int ii, int l) { return L == 1 ? ii : ((
 // tokens are walked in order in chunks: while one chunk is computed, the next chunk's k, q (dk each), the
 // block's v columns, the decay and the step size arrive in shared memory by asynchronous copies.
 // qkv row [q: G*dk | k: G*dk | v: H*dv], gb row [g: H | beta: H]; o [T, H*dv] float32.
-template <int PER, int L, int NC>
+template <int PER, int L, int NC, bool EXACT>
 __global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb,
                        const int* __restrict__ seq_slot, const int* __restrict__ cu_q,
@@ -161,7 +161,9 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
     if (slot < 0 || n <= 0) return;
     const int g = h / (H / G);
     const int C = 2 * G * dk + H * dv;
-    const int per = dk / L;
+    // EXACT: every lane keeps exactly PER rows, known at compile time (with the count only known at run time
+    // every unrolled instruction carries a predicate: a scan of 2,048 tokens then took 1.10 instead of 0.74 ms)
+    const int per = EXACT ? PER : dk / L;
     bool mine[NC];
 #pragma unroll
     for (int c = 0; c < NC; c++) mine[c] = jj + c < cols && j + c < dv;
@@ -377,7 +379,7 @@ last_rows_to_state_kernel(float* state, const T* h, int D, const int* __restrict
 // grid (H * column tiles, B), columns and lanes as in the delta rule's scan.  Staged per token: r, k, the
 // decay's argument z (turned into w = exp(-exp(z + w0)) once it has arrived), u * k, and the block's v columns.
 // r, k, v, z: float32 rows of H*d with one row stride; u, w0: [H*d].
-template <int PER, int L>
+template <int PER, int L, bool EXACT>
 __global__ void __launch_bounds__(PER >= 64 ? 256 : 512)
 decay_scan_kernel(float* o, float* state, const float* r, const float* k, const float* v, const float* z,
                   long long stride, const float* __restrict__ u, const float* __restrict__ w0,
@@ -391,7 +393,7 @@ decay_scan_kernel(float* o, float* state, const float* r, const float* k, const 
     const int slot = seq_slot[b];
     const int row0 = cu_q[b], n = cu_q[b + 1] - row0;
     if (slot < 0 || n <= 0) return;
-    const int per = d / L;
+    const int per = EXACT ? PER : d / L;
     const bool mine = jj < cols && j < d;
     const int dp = (d + 3) / 4 * 4;
     const int tokf = 4 * dp + (cols + 3) / 4 * 4;                // r, k, z -> w, u * k, v columns
@@ -545,8 +547,12 @@ int oe_delta_rule_scan(float* o, float* state, const float* qkv, const float* gb
     const dim3 grid(H * ((dv + p.cols - 1) / p.cols), n_seqs), block(((p.cols / nc) * L + 31) / 32 * 32);
 #define OE_SCAN(PER, LL) \
     if (L == LL && per <= PER) { \
-        if (nc == 2 && PER <= 16) return oe_launch(delta_rule_scan_kernel<(PER <= 16 ? PER : 16), LL, 2>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
-        return oe_launch(delta_rule_scan_kernel<PER, LL, 1>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
+        if (nc == 2 && PER <= 16) { \
+            if (per == PER) return oe_launch(delta_rule_scan_kernel<(PER <= 16 ? PER : 16), LL, 2, true>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
+            return oe_launch(delta_rule_scan_kernel<(PER <= 16 ? PER : 16), LL, 2, false>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
+        } \
+        if (per == PER) return oe_launch(delta_rule_scan_kernel<PER, LL, 1, true>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
+        return oe_launch(delta_rule_scan_kernel<PER, LL, 1, false>, grid, block, p.smem, st, o, state, qkv, gb, seq_slot, cu_q, G, H, dk, dv, p.cols, p.chunk); \
     }
     OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
     OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
@@ -590,7 +596,10 @@ int oe_decay_scan(float* o, float* state, const float* r, const float* k, const 
     const int L = p.L, per = d / L;
     const dim3 grid(H * ((d + p.cols - 1) / p.cols), n_seqs), block(p.threads);
 #define OE_SCAN(PER, LL) \
-    if (L == LL && per <= PER) return oe_launch(decay_scan_kernel<PER, LL>, grid, block, p.smem, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d, p.cols, p.chunk);
+    if (L == LL && per <= PER) { \
+        if (per == PER) return oe_launch(decay_scan_kernel<PER, LL, true>, grid, block, p.smem, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d, p.cols, p.chunk); \
+        return oe_launch(decay_scan_kernel<PER, LL, false>, grid, block, p.smem, st, o, state, r, k, v, z, stride, u, w0, seq_slot, cu_q, H, d, p.cols, p.chunk); \
+    }
     OE_SCAN(8, 8) OE_SCAN(16, 8) OE_SCAN(32, 8)
     OE_SCAN(8, 4) OE_SCAN(16, 4) OE_SCAN(32, 4) OE_SCAN(64, 4)
     OE_SCAN(8, 2) OE_SCAN(16, 2) OE_SCAN(32, 2) OE_SCAN(64, 2) OE_SCAN(128, 2)
