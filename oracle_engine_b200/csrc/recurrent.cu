@@ -181,13 +181,22 @@ delta_rule_scan_kernel(float* o, float* state, const float* qkv, const float* gb
         const int cn = min(chunk, n - c0);
         if (vec) {
             const int kq4 = dk / 2, v4 = cols / 4, vpt = kq4 + v4;        // 16-byte pieces of a token: k and q, v columns
-            for (int e = threadIdx.x; e < cn * vpt; e += blockDim.x) {
-                const int tt = e / vpt, r = e % vpt;
+            auto piece = [&](int tt, int r) {
                 const float* rowp = qkv + (size_t)(row0 + c0 + tt) * C;
                 float* d = dst + tt * tokf;
                 if (r < dk / 4) cp_async16(d + 4 * r, rowp + (size_t)(G + g) * dk + 4 * r);
                 else if (r < kq4) cp_async16(d + 4 * r, rowp + (size_t)g * dk + 4 * (r - dk / 4));
-                else if (col0 + 4 * (r - kq4) < dv) cp_async16(d + 2 * dk + 4 * (r - kq4), rowp + (size_t)2 * G * dk + (size_t)h * dv + col0 + 4 * (r - kq4));
+                else if (col0 + 4 * (r - kq4) < dv) cp_async16(d + 4 * r, rowp + (size_t)2 * G * dk + (size_t)h * dv + col0 + 4 * (r - kq4));
+            };
+            // a power-of-two group of threads per token (shifts, no division): thread (tt, r) copies piece r
+            const int lg = 32 - __clz(max(vpt - 1, 1)), span = 1 << lg;
+            if (span <= (int)blockDim.x) {
+                const int r = threadIdx.x & (span - 1);
+                if (r < vpt)
+                    for (int tt = threadIdx.x >> lg; tt < cn; tt += blockDim.x >> lg) piece(tt, r);
+            } else {
+                for (int tt = 0; tt < cn; tt++)
+                    for (int r = threadIdx.x; r < vpt; r += blockDim.x) piece(tt, r);
             }
             for (int e = threadIdx.x; e < cn * 2; e += blockDim.x)
                 cp_async4(dst + (e >> 1) * tokf + 2 * dk + cols + (e & 1), gb + (size_t)(row0 + c0 + (e >> 1)) * 2 * H + (size_t)(e & 1) * H + h);
@@ -408,14 +417,22 @@ decay_scan_kernel(float* o, float* state, const float* r, const float* k, const 
         const int cn = min(chunk, n - c0);
         if (vec) {
             const int d4 = d / 4, v4 = cols / 4, vpt = 3 * d4 + v4;      // 16-byte pieces of a token: r, k, z, v columns
-            for (int e = threadIdx.x; e < cn * vpt; e += blockDim.x) {
-                const int tt = e / vpt, q = e % vpt;
+            auto piece = [&](int tt, int q) {
                 const size_t at = (size_t)(row0 + c0 + tt) * stride + (size_t)h * d;
                 float* dd = dst + tt * tokf;
                 if (q < d4) cp_async16(dd + 4 * q, r + at + 4 * q);
                 else if (q < 2 * d4) cp_async16(dd + dp + 4 * (q - d4), k + at + 4 * (q - d4));
                 else if (q < 3 * d4) cp_async16(dd + 2 * dp + 4 * (q - 2 * d4), z + at + 4 * (q - 2 * d4));
                 else if (col0 + 4 * (q - 3 * d4) < d) cp_async16(dd + 4 * dp + 4 * (q - 3 * d4), v + at + col0 + 4 * (q - 3 * d4));
+            };
+            const int lg = 32 - __clz(max(vpt - 1, 1)), span = 1 << lg;
+            if (span <= (int)blockDim.x) {
+                const int q = threadIdx.x & (span - 1);
+                if (q < vpt)
+                    for (int tt = threadIdx.x >> lg; tt < cn; tt += blockDim.x >> lg) piece(tt, q);
+            } else {
+                for (int tt = 0; tt < cn; tt++)
+                    for (int q = threadIdx.x; q < vpt; q += blockDim.x) piece(tt, q);
             }
             cp_async_commit();
             return;
