@@ -363,7 +363,7 @@ def fuvipel_shape(width: int, layers: int, vocab: int) -> dict:
              "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4}}
     par = {"type": "parallel", "mlp": {"kind": "dense", "ff": 4 * width},
            "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
-                              "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 500000.0}},
+                              "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 1000000.0}},
                      "right": {"heads": width // 64, "dim": 64, "rank": 64}}}
     return {"architecture": "Fuvipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
             "layers": [par if i % 4 == 3 else delta for i in range(layers)]}

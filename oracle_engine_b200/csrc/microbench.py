@@ -6,6 +6,8 @@
     python -m oracle_engine_b200.csrc.microbench attention --batch 8 --context 640 --decode warps
     python -m oracle_engine_b200.csrc.microbench norm --rows 2048 --width 3072
     python -m oracle_engine_b200.csrc.microbench rope --tokens 4096
+    python -m oracle_engine_b200.csrc.microbench scan --kind delta --tokens 2048 --batch 1 [--heads 16 --dim 128]
+    python -m oracle_engine_b200.csrc.microbench scan --kind decay --tokens 1 --batch 64 --heads 32 --dim 64
 
 In the manner of the reference's benchmark/micro_gemm.cpp (:97-128 correctness against a
 scalar double-precision product, :130-151 GFLOP/s), for the CUDA kernels of this library.
@@ -192,6 +194,52 @@ def run_rope(a):
            3.0 * T * (H + KVH) * hd, err)
 
 
+def run_scan(a):
+    """The scans of the recurrent mixers (csrc/recurrent.cu) on `batch` sequences of `tokens` tokens each, against the
+    recurrence written out in float64 for the first sequence's first head (up to 64 tokens)."""
+    dev = torch.device("cuda:0")
+    T, B, H, d = a.tokens, a.batch, a.heads, a.dim
+    ctx = SimpleNamespace(seq_slot=torch.arange(B, dtype=torch.int32, device=dev), n_seqs=B,
+                          cu_q=(torch.arange(B + 1, dtype=torch.int32, device=dev) * T).contiguous())
+    n = min(T, 64)
+    if a.kind == "delta":
+        G = max(1, H // 2)
+        C = 2 * G * d + H * d
+        qkv = torch.randn(T * B, C, device=dev) * 0.1
+        gb = torch.rand(T * B, 2 * H, device=dev) * 0.5 + 0.5
+        state = torch.zeros(B, H, d, d, device=dev)
+        o = torch.empty(T * B, H * d, device=dev)
+        ops.delta_rule_scan(o, state, qkv, gb, ctx, G, H, d, d)
+        S = torch.zeros(d, d, dtype=torch.float64)
+        err = 0.0
+        for t in range(n):
+            q, k = qkv[t, :d].double().cpu(), qkv[t, G * d:G * d + d].double().cpu()
+            v = qkv[t, 2 * G * d:2 * G * d + d].double().cpu()
+            S = gb[t, 0].item() * S
+            S = S + torch.outer(k, gb[t, H].item() * (v - S.T @ k))
+            err = max(err, (o[t, :d].double().cpu() - S.T @ q).abs().max().item())
+        us = timed(lambda i: ops.delta_rule_scan(o, state, qkv, gb, ctx, G, H, d, d), a.iters, a.once)
+        nbytes = (qkv.numel() + gb.numel() + o.numel() + 2 * state.numel()) * 4
+        report(f"delta_rule_scan tokens={T} batch={B} heads={H} ({d} x {d})", us, nbytes, 6.0 * T * B * H * d * d, err)
+        return
+    r, k, v, z = (torch.randn(T * B, H * d, device=dev) * 0.1 for _ in range(4))
+    u, w0 = torch.randn(H * d, device=dev), torch.randn(H * d, device=dev) - 3
+    state = torch.zeros(B, H, d, d, device=dev)
+    o = torch.empty(T * B, H * d, device=dev)
+    ops.decay_scan(o, state, r, k, v, z, u, w0, ctx, H, d)
+    S = torch.zeros(d, d, dtype=torch.float64)
+    err = 0.0
+    for t in range(n):
+        rr, kk, vv = (x[t, :d].double().cpu() for x in (r, k, v))
+        w = torch.exp(-torch.exp(z[t, :d].double().cpu() + w0[:d].double().cpu()))
+        kv = torch.outer(kk, vv)
+        err = max(err, (o[t, :d].double().cpu() - (S + u[:d].double().cpu()[:, None] * kv).T @ rr).abs().max().item())
+        S = w[:, None] * S + kv
+    us = timed(lambda i: ops.decay_scan(o, state, r, k, v, z, u, w0, ctx, H, d), a.iters, a.once)
+    nbytes = (5 * r.numel() + 2 * state.numel()) * 4
+    report(f"decay_scan tokens={T} batch={B} heads={H} ({d} x {d})", us, nbytes, 4.0 * T * B * H * d * d, err)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="what", required=True)
@@ -233,12 +281,18 @@ def main(argv=None):
     r.add_argument("--heads", type=int, default=24)
     r.add_argument("--kv-heads", type=int, default=8)
     r.add_argument("--head-dim", type=int, default=128)
-    for p in (g, at, n, r):
+    sc = sub.add_parser("scan")
+    sc.add_argument("--kind", default="delta", choices=["delta", "decay"])
+    sc.add_argument("--tokens", type=int, default=2048)
+    sc.add_argument("--batch", type=int, default=1)
+    sc.add_argument("--heads", type=int, default=16)
+    sc.add_argument("--dim", type=int, default=128)
+    for p in (g, at, n, r, sc):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--once", action="store_true", help="run without graph or timing (for a profiler)")
     a = ap.parse_args(argv)
     ops.require_cuda()
-    {"gemm": run_gemm, "attention": run_attention, "norm": run_norm, "rope": run_rope}[a.what](a)
+    {"gemm": run_gemm, "attention": run_attention, "norm": run_norm, "rope": run_rope, "scan": run_scan}[a.what](a)
     return 0
 
 

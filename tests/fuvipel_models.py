@@ -50,9 +50,9 @@ SHARP = config(200, 64, 1e-5, [
 
 # head sizes of real models (128 and 64: the tensor-memory prompt attention; 128 x 128 and 64 x 64 states)
 REAL = config(1000, 1024, 1e-6, [
-    parallel(8, 2, 128, 0.0884, {"dims": 64, "base": 500000.0}, 16, 64, 32, ff=2048),
+    parallel(8, 2, 128, 0.0884, {"dims": 96, "base": 250000.0}, 16, 64, 32, ff=2048),
     delta(8, 4, 128, 128, 4),
-    parallel(6, 6, 64, 0.125, {"dims": 64, "base": 10000.0}, 4, 128, 16)])
+    parallel(6, 6, 64, 0.11, {"dims": 48, "base": 10000.0}, 4, 128, 16)])
 
 ALL = {"F1": (F1, 3), "F2": (F2, 4), "F3": (F3, 5), "F4": (F4, 7), "SHARP": (SHARP, 6)}
 
