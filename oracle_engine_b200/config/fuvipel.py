@@ -9,7 +9,7 @@ config.json of this design:
       delta        mixer: heads, kv_heads, dim, vdim, conv
       parallel     mixer: left {heads, kv_heads, dim, vdim, scale, rot {dims, base} or null},
                           right {heads, dim, optionally rank}
-Nothing else is read, and every key is checked.  The design has no largest position, no stop tokens and
+Nothing else is read; every key below the top level is checked, an unknown one is refused.  The design has no largest position, no stop tokens and
 a head tied to the embedding table.
 """
 from __future__ import annotations
@@ -83,7 +83,8 @@ class FuvipelConfig:
     @staticmethod
     def from_dict(raw: dict) -> "FuvipelConfig":
         r = _Reader(raw)
-        _only(raw, "(top level)", ("architecture", "architectures", "vocab", "width", "norm", "layers", "torch_dtype"))
+        # top-level keys beyond these are a file's own notes (a name, a seed, a dtype) and are not read; inside
+        # `norm`, a layer, a mixer or a feed-forward an unknown key would be a mechanism this code does not have
         norm = _obj(raw.get("norm"), "norm")
         _only(norm, "norm", ("eps",))
         layers = raw.get("layers")

@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int MAX_TAPS = 16;
+constexpr int MAX_TAPS = 32;
 constexpr int MAX_CHUNK = 16;       // tokens whose vectors are staged at once (fewer where they are long)
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {

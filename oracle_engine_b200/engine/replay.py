@@ -27,6 +27,25 @@ import numpy as np
 
 SLACK_REQUESTS = 64       # live requests whose last, partly filled page the cache has room for beyond --max-tokens
 MAX_SLOTS = 1024          # the most requests a replay holds at once
+STATE_BUDGET_BYTES = 8 << 30     # ... fewer where the per-request state of recurrent layers would take more than this
+
+
+def state_bytes_per_slot(folder) -> int:
+    """Bytes of fixed-size state one request keeps (recurrent and convolutional mixers), from config.json alone."""
+    import torch
+    from ..config.base import load_config
+    from ..parts.model import DecoderModel
+    from .runtime import Runtime
+    config, arch = load_config(folder)
+    model = DecoderModel(arch.build_spec(config), Runtime(torch.float32, torch.device("cpu")))
+    total = 0
+    for needs in model.state_needs():
+        for need in needs.values():
+            n = torch.empty((), dtype=need.dtype).element_size()
+            for d in need.shape:
+                n *= int(d)
+            total += n
+    return total
 
 
 def replay(engine, lines, out_dir: Path, log=sys.stdout) -> int:
@@ -81,8 +100,9 @@ def main(argv=None) -> int:
     # SLACK_REQUESTS such pages is added to what the trace says its requests hold.  A model with recurrent
     # layers keeps a state per slot, so the slots are bounded too.
     tokens = int(args.max_tokens) + SLACK_REQUESTS * PAGE
+    slots = min(MAX_SLOTS, max(1, tokens // PAGE), max(8, STATE_BUDGET_BYTES // max(1, state_bytes_per_slot(args.model))))
     engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=tokens, max_seq_len=tokens,
-                                    n_slots=min(MAX_SLOTS, max(1, tokens // PAGE)), use_graphs=not args.no_graphs)
+                                    n_slots=slots, use_graphs=not args.no_graphs)
     replay(engine, sys.stdin, Path(args.out))
     return 0
 

@@ -44,8 +44,8 @@ class GatedDelta(Part):
         self.eps = float(self._need("eps"))
         if self.H % self.G:
             raise ValueError(f"gated_delta: {self.H} heads are not a multiple of {self.G} key heads")
-        if not (1 <= self.dk <= 256 and 1 <= self.dv <= 4096 and 1 <= self.taps <= 16):
-            raise ValueError("gated_delta: key_dim up to 256, value_dim up to 4096 and 1..16 taps are supported")
+        if not (1 <= self.dk <= 256 and 1 <= self.dv <= 4096 and 1 <= self.taps <= 32):
+            raise ValueError("gated_delta: key_dim up to 256, value_dim up to 4096 and 1..32 taps are supported")
         self.C = 2 * self.G * self.dk + self.H * self.dv                    # channels that pass the convolution
         self.P = self.C + self.H * self.dv + 2 * self.H                     # + gate, beta, a
         self.names = {k: prefix + v for k, v in {**_NAMES, **self.params.get("tensor_names", {})}.items()}

@@ -43,6 +43,10 @@ F4 = config(97, 72, 2e-5, [
     delta(3, 1, 15, 10, 6),
     parallel(2, 1, 34, 0.2, {"dims": 10, "base": 1000.0}, 3, 30, 5, ff=50),
     delta(2, 2, 8, 70, 2, ff=36)])
+# one kind of layer only: a model without any paged cache, and one without delta layers
+DELTA_ONLY = config(150, 64, 1e-5, [delta(2, 1, 16, 24, 3, ff=80), delta(4, 4, 8, 8, 4)])
+PARALLEL_ONLY = config(150, 64, 1e-5, [parallel(2, 2, 16, 0.4, {"dims": 8, "base": 300.0}, 2, 16, 4, ff=80),
+                                       parallel(4, 1, 32, 0.2, None, 1, 32, 8)])
 # peaked attention: one key decides a query's output, so a key that is lost or wrong shows
 SHARP = config(200, 64, 1e-5, [
     parallel(4, 2, 32, 1.0, {"dims": 32, "base": 10000.0}, 2, 32, 8),
@@ -54,7 +58,8 @@ REAL = config(1000, 1024, 1e-6, [
     delta(8, 4, 128, 128, 4),
     parallel(6, 6, 64, 0.11, {"dims": 48, "base": 10000.0}, 4, 128, 16)])
 
-ALL = {"F1": (F1, 3), "F2": (F2, 4), "F3": (F3, 5), "F4": (F4, 7), "SHARP": (SHARP, 6)}
+ALL = {"F1": (F1, 3), "F2": (F2, 4), "F3": (F3, 5), "F4": (F4, 7), "SHARP": (SHARP, 6), "DELTA_ONLY": (DELTA_ONLY, 8),
+       "PARALLEL_ONLY": (PARALLEL_ONLY, 9)}
 
 
 def write(folder, raw, seed, std=0.1, long_memory=True):

@@ -17,6 +17,8 @@ def test_config_round_trip_and_refusals():
         cfg = FuvipelConfig.from_dict(raw)
         assert FuvipelConfig.from_dict(json.loads(json.dumps(cfg.to_dict()))) == cfg
         assert cfg.vocab == raw["vocab"] and cfg.width == raw["width"] and cfg.norm_eps == raw["norm"]["eps"]
+    noted = dict(copy.deepcopy(fm.F1), seed=3, name="a note")          # a file's own notes at the top level are not read
+    assert FuvipelConfig.from_dict(noted) == FuvipelConfig.from_dict(fm.F1)
     bad = copy.deepcopy(fm.F1)
     bad["layers"][1]["type"] = "conv"
     with pytest.raises(ConfigError, match="type"):

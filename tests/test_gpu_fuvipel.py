@@ -127,6 +127,22 @@ def test_whole_decoded_pieces_and_batches_agree_with_plain(models, tmp_path, nam
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["DELTA_ONLY", "PARALLEL_ONLY"])
+def test_models_of_one_kind_of_layer(models, tmp_path, name, dtype):
+    """Only recurrent layers (no paged cache at all) and only parallel layers: prompts, decoding, a ragged batch."""
+    folder, plain = models[name]
+    lens = [70, 3, 130]
+    requests = [helpers.random_tokens(n, plain.cfg["vocab"], 610 + i) for i, n in enumerate(lens)]
+    eng = _engine(folder, dtype, max_tokens=512)
+    assert len(eng.cache.groups) == (0 if name == "DELTA_ONLY" else 2)         # two attentions of different key sizes
+    for k, steps in {"tail": helpers.tail_steps(requests, 10), "batched": helpers.batched_steps(requests, [60, 1, 66], 3)}.items():
+        got = helpers.collect(steps, helpers.TraceRunner(eng, tmp_path / k).run(steps), requests)
+        _compare(got, plain, requests, TOL[dtype], f"{name} {dtype} {k}")
+    eng.cache.check()
+    assert eng.cache.slots.n_free == eng.cache.n_slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_far_keys_and_page_borders_under_a_peaked_softmax(models, tmp_path, dtype):
     """Prompts that end just before, at and just after a page border, decoded across the next one, with an
     attention in which single keys (far ones too) decide: a lost or misplaced key changes the logits."""
@@ -170,6 +186,14 @@ def test_real_head_sizes(tmp_path, dtype):
     for k, steps in runs.items():
         got = helpers.collect(steps, helpers.TraceRunner(eng, tmp_path / k).run(steps), requests)
         _compare(got, plain, requests, TOL[dtype], f"REAL {dtype} {k}")
+    # decoding over a handful of keys, where the sink is a large share of the softmax's denominator: one request
+    # and three together, from the first token on (the decode kernels, with and without split keys)
+    short = [r[:9] for r in requests]
+    for k, steps in {"short_alone": helpers.tail_steps(short[:1], 1000),
+                     "short_batch": helpers.batched_steps(short, [1, 2, 3], 3)}.items():
+        reqs = short[:1] if k == "short_alone" else short
+        got = helpers.collect(steps, helpers.TraceRunner(eng, tmp_path / k).run(steps), reqs)
+        _compare(got, plain, reqs, TOL[dtype], f"REAL {dtype} {k}")
     eng.check_device_errors()
     eng.cache.check()
 
