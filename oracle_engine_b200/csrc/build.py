@@ -36,6 +36,9 @@ LIBRARIES = {
     "sampling": ("sampling.cu", []),
     "rowwise": ("rowwise.cu", []),
     "recurrent": ("recurrent.cu", []),
+    "attention_split": ("attention_split.cu", []),
+    "retention": ("retention.cu", []),
+    "moe": ("moe.cu", []),
     "gemm_tc": ("gemm_tcgen05.cu", []),
     "gemm_pair": ("gemm_tcgen05_pair.cu", []),
     "gemm_skinny": ("gemm_skinny.cu", []),

@@ -52,6 +52,18 @@ _SIGNATURES = {
         "oe_tanh_rows": [_P, _P, _L, _P],
         "oe_head_gate": [_P, _P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _P],
         "oe_rot_norm_kv_write": [_P, _L, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+        "oe_scaled_add": [_P, _P, _P, _P, _F, _F, _F, _L, _I, _P],
+    },
+    "attention_split": {
+        "oe_rope_split_kv_write": [_P, _L, _P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "oe_attn_split": [_P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    },
+    "retention": {
+        "oe_retention_scan": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    },
+    "moe": {
+        "oe_moe_route": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _P],
+        "oe_moe_dense_act": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
     },
     "recurrent": {
         "oe_short_conv_prepare": [_P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
@@ -68,7 +80,8 @@ _SIGNATURES = {
     },
 }
 _TYPED = {"oe_embed_gather", "oe_rmsnorm", "oe_rope_kv_write", "oe_swiglu", "oe_gemm_simple", "oe_attn_paged",
-          "oe_relu2", "oe_tanh_rows", "oe_rot_norm_kv_write", "oe_token_shift_mix", "oe_last_rows_to_state"}
+          "oe_relu2", "oe_tanh_rows", "oe_rot_norm_kv_write", "oe_token_shift_mix", "oe_last_rows_to_state",
+          "oe_rope_split_kv_write", "oe_attn_split", "oe_moe_dense_act"}
 _fn_cache: dict[str, object] = {}
 
 
@@ -346,6 +359,145 @@ def rot_norm_kv_write(qk: torch.Tensor, inv_freq: torch.Tensor | None, rot_dims:
         _ptr(qk), qk.stride(0), _ptr(inv_freq), int(rot_dims), _ptr(cache), _ptr(tables), tables.shape[1],
         _ptr(tok_seq), _ptr(tok_pos), qk.shape[0], n_heads, n_kv_heads, head_dim, float(eps), int(bool(has_kv)),
         _stream()), "rot_norm_kv_write")
+
+
+def scaled_add(dst: torch.Tensor, y0: torch.Tensor, vec: torch.Tensor | None = None, mult: float = 1.0,
+               c0: float = 1.0, y1: torch.Tensor | None = None, c1: float = 0.0) -> None:
+    """dst += mult * vec * (c0 y0 + c1 y1); all float32 and contiguous, vec one value per column (or None: ones)."""
+    _dev(dst, y0, y1, vec)
+    for t, n in ((dst, "dst"), (y0, "y0")) + (((y1, "y1"),) if y1 is not None else ()) + \
+            (((vec, "vec"),) if vec is not None else ()):
+        _f32c(t, n)
+    rows, D = dst.shape
+    if y0.shape != dst.shape or (y1 is not None and y1.shape != dst.shape) or (vec is not None and vec.numel() != D):
+        raise KernelError("scaled_add: y0 and y1 of dst's shape and vec of its width expected")
+    _check(_fn("rowwise", "oe_scaled_add")(_ptr(dst), _ptr(y0), _ptr(y1), _ptr(vec), float(mult), float(c0), float(c1),
+                                           rows, D, _stream()), "scaled_add")
+
+
+# ---------------------------------------------------------------------------------------- attention_split.cu
+
+def _split_cache_ok(kcache, vcache, dtype, G, dk, dv) -> bool:
+    return (kcache is not None and vcache is not None and kcache.dtype == dtype and vcache.dtype == dtype
+            and kcache.is_contiguous() and vcache.is_contiguous()
+            and tuple(kcache.shape[1:]) == (G, PAGE, dk) and tuple(vcache.shape[1:]) == (G, PAGE, dv))
+
+
+def rope_split_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, rot_dims: int,
+                        kcache: torch.Tensor | None, vcache: torch.Tensor | None, tables: torch.Tensor,
+                        tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int, n_kv_heads: int, dk: int, dv: int,
+                        has_kv: bool = True) -> None:
+    """Turns the first rot_dims dimensions of every q head (in place) and k head (dimension i < rot_dims/2 with
+    i + rot_dims/2) by the token's position, and writes k to the key tensor and v to the value tensor of the cache.
+
+    qkv [T, >= H dk + G dk + G dv]; cos/sin float32 [positions, rot_dims/2]; kcache [pages, G, PAGE, dk],
+    vcache [pages, G, PAGE, dv] of qkv's dtype; tok_seq < 0 marks a padding row."""
+    _dev(qkv, cos, sin, kcache, vcache, tables, tok_seq, tok_pos)
+    for t, n in ((tables, "tables"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
+        _i32(t, n)
+    width = n_heads * dk + (n_kv_heads * (dk + dv) if has_kv else 0)
+    if qkv.shape[1] < width or qkv.stride(1) != 1:
+        raise KernelError(f"rope_split_kv_write: qkv needs at least {width} contiguous columns")
+    if rot_dims:
+        _f32c(cos, "cos")
+        _f32c(sin, "sin")
+        if rot_dims % 2 or rot_dims > dk or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
+            raise KernelError("rope_split_kv_write: cos/sin must be [positions, rot_dims/2], rot_dims even and <= dk")
+    if has_kv and not _split_cache_ok(kcache, vcache, qkv.dtype, n_kv_heads, dk, dv):
+        raise KernelError("rope_split_kv_write: the cache must be [pages, G, PAGE, dk] and [pages, G, PAGE, dv] of qkv's dtype")
+    _check(_fn("attention_split", "oe_rope_split_kv_write", qkv.dtype)(
+        _ptr(qkv), qkv.stride(0), _ptr(cos), _ptr(sin), int(rot_dims), _ptr(kcache), _ptr(vcache), _ptr(tables),
+        tables.shape[1], _ptr(tok_seq), _ptr(tok_pos), qkv.shape[0], n_heads, n_kv_heads, dk, dv, int(bool(has_kv)),
+        _stream()), "rope_split_kv_write")
+
+
+def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, tables: torch.Tensor,
+               tok_seq: torch.Tensor, tok_pos: torch.Tensor, n_heads: int, n_kv_heads: int, dk: int, dv: int,
+               window: int, scale: float, cap: float = 0.0) -> None:
+    """out[t] = softmax attention of token t's query heads over the keys (pos - window, pos] of its sequence, with
+    s <- cap tanh(s / cap) when cap > 0.  q [T, >= H dk] (row stride free), out contiguous [T, H dv]."""
+    _dev(out, q, kcache, vcache, tables, tok_seq, tok_pos)
+    for t, n in ((tables, "tables"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
+        _i32(t, n)
+    if out.shape[1] != n_heads * dv or not out.is_contiguous() or q.stride(1) != 1 or q.dtype != out.dtype \
+            or q.shape[1] < n_heads * dk:
+        raise KernelError("attn_split: out must be contiguous [T, H dv] and q of its dtype with at least H dk columns")
+    if not _split_cache_ok(kcache, vcache, out.dtype, n_kv_heads, dk, dv):
+        raise KernelError("attn_split: the cache must be [pages, G, PAGE, dk] and [pages, G, PAGE, dv] of out's dtype")
+    _check(_fn("attention_split", "oe_attn_split", out.dtype)(
+        _ptr(out), _ptr(q), q.stride(0), _ptr(kcache), _ptr(vcache), _ptr(tables), tables.shape[1], _ptr(tok_seq),
+        _ptr(tok_pos), out.shape[0], n_heads, n_kv_heads, dk, dv, int(window), float(scale), float(cap or 0.0),
+        _stream()), "attn_split")
+
+
+# ---------------------------------------------------------------------------------------- retention.cu
+
+def retention_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off_q: int, off_k: int, off_v: int,
+                   cos: torch.Tensor | None, sin: torch.Tensor | None, rot_dims: int, k_scale: float,
+                   decay: torch.Tensor, ctx, heads: int, dk: int, dv: int) -> None:
+    """Per sequence and head, over the step's tokens in order: S <- decay_h S + k v^T; o = S^T q, with q and k
+    turned by the token's position (first rot_dims dimensions, halves paired) and k times k_scale.  proj float32
+    [T, >= ...] holds q at column off_q (H dk values), k at off_k (H dk), v at off_v (H dv); state float32
+    [slots, H, dk, dv] is read and written; o float32 [T, H dv]."""
+    _dev(o, state, proj, cos, sin, decay)
+    for t, n in ((o, "o"), (state, "state"), (decay, "decay")):
+        _f32c(t, n)
+    T = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1:
+        raise KernelError("retention_scan: proj must be float32 with contiguous rows")
+    if tuple(state.shape[1:]) != (heads, dk, dv) or tuple(o.shape) != (T, heads * dv) or decay.numel() != heads \
+            or max(off_q + heads * dk, off_k + heads * dk, off_v + heads * dv) > proj.shape[1]:
+        raise KernelError("retention_scan: shapes do not agree")
+    if rot_dims:
+        _f32c(cos, "cos")
+        _f32c(sin, "sin")
+        if rot_dims % 2 or rot_dims > dk or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
+            raise KernelError("retention_scan: cos/sin must be [positions, rot_dims/2], rot_dims even and <= dk")
+    _check(_fn("retention", "oe_retention_scan")(
+        _ptr(o), _ptr(state), _ptr(proj), proj.stride(0), int(off_q), int(off_k), int(off_v), _ptr(cos), _ptr(sin),
+        int(rot_dims), float(k_scale), _ptr(decay), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), _ptr(ctx.tok_pos), ctx.n_seqs,
+        heads, dk, dv, _stream()), "retention_scan")
+
+
+# ---------------------------------------------------------------------------------------- moe.cu
+
+def moe_route(z: torch.Tensor, n_experts: int, top: int, has_gate: bool, dense: torch.Tensor, tok_seq: torch.Tensor,
+              idx: torch.Tensor | None = None, wt: torch.Tensor | None = None) -> None:
+    """From router logits z float32 [T, >= E (+ 1)]: dense [T, E (+ 1)] float32 gets each chosen expert's weight
+    (softmax over the `top` largest logits alone; zero elsewhere) and, with has_gate, sigmoid of column E in its
+    last column; idx int32 [T, top] and wt float32 [T, top] receive the choice itself when given."""
+    _dev(z, dense, tok_seq, idx, wt)
+    _i32(tok_seq, "tok_seq")
+    _f32c(dense, "dense")
+    T = z.shape[0]
+    W = n_experts + int(bool(has_gate))
+    if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < W or tuple(dense.shape) != (T, W):
+        raise KernelError("moe_route: z float32 [T, >= E (+1)] and dense [T, E (+1)] expected")
+    if top > n_experts:
+        raise KernelError("moe_route: more experts chosen than there are")
+    if idx is not None:
+        _i32(idx, "idx")
+    if wt is not None:
+        _f32c(wt, "wt")
+    for t in (idx, wt):
+        if t is not None and tuple(t.shape) != (T, top):
+            raise KernelError("moe_route: idx and wt must be [T, top]")
+    _check(_fn("moe", "oe_moe_route")(_ptr(z), z.stride(0), n_experts, top, int(bool(has_gate)), _ptr(idx), _ptr(wt),
+                                      _ptr(dense), _ptr(tok_seq), T, _stream()), "moe_route")
+
+
+def moe_dense_act(a: torch.Tensor, gu: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int) -> None:
+    """a[t, c] = silu(gu[t, c]) * gu[t, F + c] * dense[t, group of c]; the group of column c is c // ff for the
+    first n_experts * ff columns and the last column of dense for the rest (the shared expert)."""
+    _dev(a, gu, dense)
+    _f32c(dense, "dense")
+    T, F = a.shape
+    if tuple(gu.shape) != (T, 2 * F) or gu.dtype != a.dtype or not (gu.is_contiguous() and a.is_contiguous()) \
+            or dense.shape[0] != T or dense.shape[1] < n_experts or F < n_experts * ff \
+            or (F > n_experts * ff and dense.shape[1] != n_experts + 1):
+        raise KernelError("moe_dense_act: shapes do not agree")
+    _check(_fn("moe", "oe_moe_dense_act", a.dtype)(_ptr(a), _ptr(gu), _ptr(dense), T, F, n_experts, ff, dense.shape[1],
+                                                   _stream()), "moe_dense_act")
 
 
 # ---------------------------------------------------------------------------------------- recurrent.cu

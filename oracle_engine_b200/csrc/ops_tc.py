@@ -564,3 +564,10 @@ def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
         int(window), float(scale), n_splits, None if partial is None else partial.data_ptr(),
         _attn_counters(out.device).data_ptr(), ops._stream())
     ops._check(code, "attention_decode_fused", {"splits": n_splits})
+
+
+# ---------------------------------------------------------------------------------------- keys and values of two sizes
+
+def attention_split_supported(dk: int, dv: int, n_heads: int, n_kv_heads: int) -> bool:
+    """Whether a tensor-core kernel takes an attention whose keys and values have head sizes of their own."""
+    return False

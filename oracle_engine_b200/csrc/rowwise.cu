@@ -9,6 +9,9 @@
 //   rot_norm_kv_write  q, k rotated on pairs (2i, 2i+1) of their first `dims` dimensions, then divided
 //                      by their root mean square; k goes to the cache's key rows, the k as projected
 //                      to its value rows (an attention whose values are its unrotated keys)
+//   scaled_add         dst += mult * vec * (c0 y0 + c1 y1)   (all float32; vec one value per column or null,
+//                      y1 may be null): a sublayer's output, or the weighted sum of two, times a per-channel
+//                      scale and a constant, added to the residual stream
 //
 // All arithmetic is float32; T is the type of activations and cache.  A row's result depends on
 // that row only, and every sum has a fixed order.
@@ -229,9 +232,33 @@ int rot_norm_launch(T* qk, long long row_stride, const float* inv_freq, int rot_
                      cache, tables, max_pages, tok_seq, tok_pos, n_tokens, H, KVH, hd, eps, has_kv);
 }
 
+
+__global__ void __launch_bounds__(256)
+scaled_add_kernel(float* dst, const float* y0, const float* y1, const float* __restrict__ vec, float mult, float c0,
+                  float c1, size_t total, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = c0 * y0[i];
+        if (y1) v = fmaf(c1, y1[i], v);
+        const float sc = vec ? mult * vec[i % D] : mult;
+        dst[i] = fmaf(sc, v, dst[i]);
+    }
+}
+
 }  // namespace
 
 extern "C" {
+
+int oe_scaled_add(float* dst, const float* y0, const float* y1, const float* vec, float mult, float c0, float c1,
+                  long long rows, int D, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (D < 1) return OE_ERR_UNSUPPORTED;
+    const size_t total = (size_t)rows * D;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    return oe_launch(scaled_add_kernel, dim3((unsigned)blocks), dim3(256), 0, st, dst, y0, y1, vec, mult, c0, c1, total, D);
+}
 
 int oe_cast_rows_bf16(bf16* y, const float* x, long long total, cudaStream_t st) {
     if (total <= 0) return 0;

@@ -47,3 +47,15 @@ def attend(rt, out, qkv, cache, ctx, H, KVH, hd, window, scale, sink: bool = Fal
             ops_tc.attention(out, qkv, cache.kv, cache.tables, ctx, H, KVH, hd, window, scale, sink)
             return
     ops.attn_paged(out, qkv, cache.kv, cache.tables, ctx.tok_seq, ctx.tok_pos, H, KVH, hd, window, scale, sink)
+
+
+def split_mixer_core(rt, out, qkv, cos, sin, rot, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap) -> None:
+    """Rotation, cache write and attention of an attention mixer whose keys and values have head sizes of their
+    own and lie in two cache tensors, with a cap on the scores (parts/capped_attention.py)."""
+    ops.rope_split_kv_write(qkv, cos, sin, rot, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, True)
+    if rt.dtype == torch.bfloat16 and rt.tensor_cores:
+        from ..csrc import ops_tc
+        if ops_tc.attention_split_supported(dk, dv, H, G):
+            ops_tc.attention_split(out, qkv, kcache, vcache, tables, ctx, H, G, dk, dv, window, scale, cap)
+            return
+    ops.attn_split(out, qkv, kcache, vcache, tables, ctx.tok_seq, ctx.tok_pos, H, G, dk, dv, window, scale, cap)

@@ -15,6 +15,7 @@ from .spec import ModelSpec, TensorDecl
 # importing the modules registers the built-in parts
 from . import attention, block, embedding, feedforward, norms, positions  # noqa: F401,E402
 from . import delta_rule, parallel, sink_attention, time_mix  # noqa: F401,E402
+from . import capped_attention, moe, retention  # noqa: F401,E402
 
 
 class DecoderModel:
@@ -40,6 +41,9 @@ class DecoderModel:
             FEED_FORWARDS.get(ls.feed_forward.kind)(ls.feed_forward.params, ls.prefix, self.rt)
         mnorm = NORMS.get(ls.mixer_norm.kind)(ls.mixer_norm.params, ls.prefix, self.rt)
         fnorm = None if ls.ffn_norm is None else NORMS.get(ls.ffn_norm.kind)(ls.ffn_norm.params, ls.prefix, self.rt)
+        if ls.block_params:           # an arrangement with constants or weights of its own is built like a part
+            return BLOCKS.get(ls.block)(mixer, ffn, mnorm, fnorm, params=ls.block_params, prefix=ls.prefix,
+                                        runtime=self.rt)
         return BLOCKS.get(ls.block)(mixer, ffn, mnorm, fnorm)
 
     # ------------------------------------------------------------------ weights

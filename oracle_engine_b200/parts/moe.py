@@ -1,0 +1,96 @@
+"""Feed-forward `moe_swiglu`: a mixture of experts with an optional shared expert.
+
+    z = Wr h (float32);  the `top` experts with the largest z are chosen, their weights w_e are the softmax over the
+    chosen z alone;  E_e(h) = Wdown_e (silu(Wgate_e h) * (Wup_e h));
+    y = sum_chosen w_e E_e(h) + sigmoid(Wsg h) * E_shared(h)                   (the second term only with a shared expert)
+
+How it is computed: the experts stand side by side.  One product with all gate and up matrices (the shared expert's
+behind the routed ones), one kernel that applies silu(gate) * up and multiplies each expert's columns by the token's
+weight for that expert (zero where it was not chosen, sigmoid(Wsg h) for the shared one), and one product with all
+down matrices side by side, which sums the chosen experts in its float32 accumulators.  The router and the shared
+gate are one small float32 product.  No token is moved and nothing depends on the host, so a step is the same
+kernels whatever the routing (and can be captured in a graph); the price is the products of the experts a token
+did not choose, experts / top times the arithmetic of the chosen ones, while the weights read are the same as
+soon as a step's tokens choose every expert between them.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .linear import matmul_nt
+from .registry import FEED_FORWARDS, Part
+from .spec import TensorDecl
+
+
+@FEED_FORWARDS.register("moe_swiglu")
+class MoESwiGLU(Part):
+    graph_safe = True
+    can_overwrite = True
+    """params: hidden_size, num_experts, top, expert_size, shared_size (0 or None: no shared expert), tensor_names
+    (optional overrides of "expert" (a format with {e}), "router", "shared", "shared_gate")."""
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.D = int(self._need("hidden_size"))
+        self.E = int(self._need("num_experts"))
+        self.top = int(self._need("top"))
+        self.ff = int(self._need("expert_size"))
+        self.sff = int(self.params.get("shared_size") or 0)
+        if not 1 <= self.top <= self.E:
+            raise ValueError(f"moe_swiglu: top {self.top} of {self.E} experts")
+        if self.E > 1024:
+            raise ValueError("moe_swiglu: up to 1,024 experts are supported")
+        names = {"expert": "mlp.e{e}.", "router": "mlp.router", "shared": "mlp.shared.", "shared_gate": "mlp.shared.sg",
+                 **self.params.get("tensor_names", {})}
+        self.names = {k: prefix + v for k, v in names.items()}
+        self.F = self.E * self.ff + self.sff
+        self.w_route = self.w_gu = self.w_down = None
+
+    def _expert_names(self):
+        out = [self.names["expert"].format(e=e) for e in range(self.E)]
+        return out + ([self.names["shared"]] if self.sff else [])
+
+    def tensors(self):
+        out = []
+        for i, p in enumerate(self._expert_names()):
+            f = self.ff if i < self.E else self.sff
+            out += [TensorDecl(p + "gate", (f, self.D)), TensorDecl(p + "up", (f, self.D)),
+                    TensorDecl(p + "down", (self.D, f))]
+        out.append(TensorDecl(self.names["router"], (self.E, self.D)))
+        if self.sff:
+            out.append(TensorDecl(self.names["shared_gate"], (1, self.D)))
+        return out
+
+    def load(self, get):
+        to = self.rt.to_compute
+        ex = self._expert_names()
+        self.w_gu = torch.cat([to(get(p + "gate")) for p in ex] + [to(get(p + "up")) for p in ex], 0).contiguous()
+        self.w_down = torch.cat([to(get(p + "down")) for p in ex], 1).contiguous()
+        route = [to(get(self.names["router"]))] + ([to(get(self.names["shared_gate"]))] if self.sff else [])
+        self.w_route = torch.cat(route, 0).contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_gu, self.w_down, self.w_route) if t is not None)
+
+    def flops(self, start, count):
+        return count * 2.0 * self.D * (3 * self.F + self.w_route_rows())
+
+    def w_route_rows(self):
+        return self.E + (1 if self.sff else 0)
+
+    def first_weights(self):
+        return self.w_gu
+
+    def forward(self, h, residual, ctx, overwrite: bool = False):
+        """overwrite: the output is written into `residual` (float32) instead of added."""
+        T, W = h.shape[0], self.w_route_rows()
+        z = self.rt.buffer("moe.z", T, W, dtype=torch.float32)
+        ops.gemm_simple(z, h, self.w_route)                     # float32 sums in k order, whatever the path
+        dense = self.rt.buffer("moe.dense", T, W, dtype=torch.float32)
+        ops.moe_route(z, self.E, self.top, bool(self.sff), dense, ctx.tok_seq)
+        gu = self.rt.buffer("moe.gu", T, 2 * self.F)
+        matmul_nt(self.rt, gu, h, self.w_gu)
+        a = self.rt.buffer("moe.a", T, self.F)
+        ops.moe_dense_act(a, gu, dense, self.E, self.ff)
+        matmul_nt(self.rt, residual, a, self.w_down, accumulate=not overwrite)

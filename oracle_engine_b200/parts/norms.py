@@ -13,20 +13,24 @@ from .spec import TensorDecl
 @NORMS.register("rms_norm")
 class RMSNorm(Part):
     graph_safe = True
-    """params: size, eps, name (tensor name under the prefix)."""
+    """params: size, eps, name (tensor name under the prefix), offset (added to the stored weight: 1.0 for a
+    weight that is kept around zero, y = x / rms * (1 + w); default 0)."""
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.size = int(self._need("size"))
         self.eps = float(self._need("eps"))
         self.name = prefix + self._need("name")
+        self.offset = float(self.params.get("offset", 0.0) or 0.0)
         self.weight = None
 
     def tensors(self):
-        return [TensorDecl(self.name, (self.size,), "ones_normal")]
+        return [TensorDecl(self.name, (self.size,), "normal" if self.offset else "ones_normal")]
 
     def load(self, get):
         self.weight = self.rt.to_f32(get(self.name))
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()        # float32: the sum the design asks for
 
     def weight_bytes(self):
         return 0 if self.weight is None else self.weight.numel() * self.weight.element_size()

@@ -44,6 +44,7 @@ class LayerSpec:
     mixer_norm: PartSpec
     ffn_norm: Optional[PartSpec]
     block: str = "pre_norm"            # arrangement of the four (parts/block.py)
+    block_params: dict = field(default_factory=dict)   # an arrangement's own constants and tensor names, if it has any
 
 
 @dataclass(frozen=True)
