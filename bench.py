@@ -6,8 +6,8 @@
     python bench.py --shape 8b --workload baseline      # 32 prompts of 128..4,096 tokens, 256 steps
     python bench.py --profile [--batch 64]              # device time per kind of kernel, on standard error
     python bench.py --impl reference --steps K          # the reference's own benchmark program (CPU)
-    python bench.py --design fuvipel [--widths 1024,2048,3072] [--profile]
-                                                        # the Fuvipel design beside a Llama of equal width and depth
+    python bench.py --design fuvipel|fovirax [--widths 1024,2048,3072] [--profile]
+                                                        # that design beside a Llama of equal width and depth
 
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch (default
 8), timed on the device with CUDA events over exactly K decode steps after W warm-up
@@ -369,6 +369,27 @@ def fuvipel_shape(width: int, layers: int, vocab: int) -> dict:
             "layers": [par if i % 4 == 3 else delta for i in range(layers)]}
 
 
+def fovirax_shape(width: int, layers: int, vocab: int) -> dict:
+    """A Fovirax of real layer sizes: in every layer an attention with heads of 128 (four query heads to a key
+    head, a window of 1,024 keys, capped scores, frequencies rescaled by wavelength) beside a retention with states
+    of 64 x 128, and a mixture of 8 experts of 2/3 x width, two chosen, with a shared expert of 4/3 x width: the
+    experts a token uses have the weights of a SwiGLU of 8/3 x width.  No loop: as many distinct layers as runs."""
+    heads = width // 128
+    ff = (2 * width // 3 + 63) // 64 * 64
+    layer = {"type": "parallel",
+             "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024},
+                                "rot": {"dims": 128, "base": 500000.0,
+                                        "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+                       "left_scale": 0.5,
+                       "right": {"heads": heads, "dim": 64, "vdim": 128, "rot": {"dims": 64, "base": 10000.0},
+                                 "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * i / max(1, heads - 1)) for i in range(heads)]},
+                       "right_scale": 0.5},
+             "mlp": {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 8, "top": 2}, "shared": {"ff": 2 * ff}}}
+    return {"architecture": "Fovirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 1.0,
+            "layers": [layer] * layers}
+
+
 def llama_shape(width: int, layers: int, vocab: int) -> dict:
     """The Llama decoder of the same width, depth and vocabulary: heads of 128, four query heads to a key head,
     a SwiGLU of 8/3 x width (the same weights as a two-matrix feed-forward of 4 x width)."""
@@ -379,18 +400,21 @@ def llama_shape(width: int, layers: int, vocab: int) -> dict:
 
 
 def design_compare(args) -> int:
-    """Prefill and decode throughput of the Fuvipel design beside the Llama decoder at equal width, depth and
+    """Prefill and decode throughput of a design (--design) beside the Llama decoder at equal width, depth and
     vocabulary (random weights), one JSON line; with --profile the device time per kind of kernel instead."""
     import torch
     from oracle_engine_b200 import LlamaConfig
+    from oracle_engine_b200.config.fovirax import FoviraxConfig
     from oracle_engine_b200.config.fuvipel import FuvipelConfig
     from oracle_engine_b200.engine.engine import Engine
+    design = {"fuvipel": lambda *a: FuvipelConfig.from_dict(fuvipel_shape(*a)),
+              "fovirax": lambda *a: FoviraxConfig.from_dict(fovirax_shape(*a))}[args.design]
     pk = peaks()
     layers, vocab, context = args.layers or 8, 32000, 1024
     sizes = {}
     for width in [int(w) for w in args.widths.split(",")]:
         row = {}
-        for name, cfg in (("fuvipel", FuvipelConfig.from_dict(fuvipel_shape(width, layers, vocab))),
+        for name, cfg in ((args.design, design(width, layers, vocab)),
                           ("llama", LlamaConfig.from_dict(llama_shape(width, layers, vocab)))):
             engine = Engine.from_config(cfg, seed=SEED, dtype=args.dtype, max_tokens=64 * context + 4096,
                                         max_seq_len=4096, n_slots=64)
@@ -419,7 +443,7 @@ def design_compare(args) -> int:
             torch.cuda.empty_cache()
         sizes[str(width)] = row
     if not args.profile:
-        print(json.dumps({"design": "fuvipel beside llama at equal width, depth and vocabulary", "layers": layers,
+        print(json.dumps({"design": f"{args.design} beside llama at equal width, depth and vocabulary", "layers": layers,
                           "vocab": vocab, "dtype": args.dtype, "prefill_tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
                           "peaks": pk, "data": "synthetic token ids, random-init weights N(0, 0.02) from seed 2",
                           "sizes": sizes}))
@@ -538,7 +562,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="print device time per kind of kernel of a prompt step and a decode step on standard error, "
                          "and nothing else")
-    ap.add_argument("--design", default=None, choices=["fuvipel"],
+    ap.add_argument("--design", default=None, choices=["fuvipel", "fovirax"],
                     help="measure this design beside the Llama decoder at equal sizes instead of the headline workload")
     ap.add_argument("--widths", default="1024,2048,3072", help="model widths of --design")
     args = ap.parse_args()

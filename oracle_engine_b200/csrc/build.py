@@ -44,6 +44,7 @@ LIBRARIES = {
     "gemm_skinny": ("gemm_skinny.cu", []),
     "attention_tc": ("attention_mma.cu", []),
     "attention_tc5": ("attention_tcgen05.cu", []),
+    "attention_split_tc": ("attention_split_mma.cu", []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -169,6 +170,8 @@ def build_all(names=None, verbose: bool = True) -> list[Path]:
             jobs.extend((n, {"OE_HD": hd}) for hd in DEFAULT_HEAD_DIMS)
         elif n == "attention_tc5":
             jobs.extend((n, {"OE_HD": hd}) for hd in (64, 128))
+        elif n == "attention_split_tc":
+            jobs.extend((n, {"OE_DK": dk, "OE_DV": dv}) for dk, dv in ((64, 128), (128, 128)))
         else:
             jobs.append((n, None))
     results: dict[object, object] = {}

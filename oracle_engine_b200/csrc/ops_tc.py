@@ -8,7 +8,7 @@ on shapes only.
 from __future__ import annotations
 
 import contextlib
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -569,5 +569,44 @@ def attention_decode_fused(out, qkv, cos, sin, cache, tables, ctx, n_heads: int,
 # ---------------------------------------------------------------------------------------- keys and values of two sizes
 
 def attention_split_supported(dk: int, dv: int, n_heads: int, n_kv_heads: int) -> bool:
-    """Whether a tensor-core kernel takes an attention whose keys and values have head sizes of their own."""
-    return False
+    """Whether the tensor-core kernel (csrc/attention_split_mma.cu) takes an attention whose keys and values have
+    head sizes of their own: multiples of 16 up to 256, groups of up to 64 query heads."""
+    return (dk % 16 == 0 and dv % 16 == 0 and 16 <= dk <= 256 and 16 <= dv <= 256 and n_heads % n_kv_heads == 0
+            and n_heads // n_kv_heads <= 64)
+
+
+_split_libs: dict = {}
+
+
+def _attn_split_lib(dk: int, dv: int):
+    fn = _split_libs.get((dk, dv))
+    if fn is None:
+        lib = _build.load("attention_split_tc", defines={"OE_DK": dk, "OE_DV": dv})
+        fn = lib.oe_attn_split_mma
+        fn.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]
+        fn.restype = c_int
+        _split_libs[(dk, dv)] = fn
+    return fn
+
+
+def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_heads: int, dk: int, dv: int, window: int,
+                    scale: float, cap: float) -> None:
+    """out[t] = attention of token t's query heads over the keys (pos - window, pos] of its sequence, scores capped
+    by cap tanh(s / cap) when cap > 0; bfloat16, q rotated already (rows of q may be a view of the fused product),
+    kcache [pages, G, PAGE, dk], vcache [pages, G, PAGE, dv]."""
+    from .ops import PAGE
+    if out.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 \
+            or vcache.dtype != torch.bfloat16:
+        raise ops.KernelError("attention_split: bfloat16 tensors expected")
+    if not out.is_contiguous() or out.shape[1] != n_heads * dv or q.stride(1) != 1 or q.shape[1] < n_heads * dk \
+            or q.stride(0) % 2 or q.data_ptr() % 4:
+        raise ops.KernelError("attention_split: out contiguous [T, H dv]; q rows of at least H dk values, 4-byte aligned")
+    if tuple(kcache.shape[1:]) != (n_kv_heads, PAGE, dk) or tuple(vcache.shape[1:]) != (n_kv_heads, PAGE, dv) \
+            or not (kcache.is_contiguous() and vcache.is_contiguous()):
+        raise ops.KernelError("attention_split: the cache must be [pages, G, PAGE, dk] and [pages, G, PAGE, dv]")
+    code = _attn_split_lib(dk, dv)(out.data_ptr(), q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+                                   tables.data_ptr(), tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(),
+                                   ctx.seq_qlen.data_ptr(), ctx.n_seqs, int(ctx.max_qlen), n_heads, n_kv_heads, int(window),
+                                   float(scale), float(cap or 0.0), ops._stream())
+    ops._check(code, "attention_split_mma")

@@ -86,7 +86,7 @@ class MoESwiGLU(Part):
         """overwrite: the output is written into `residual` (float32) instead of added."""
         T, W = h.shape[0], self.w_route_rows()
         z = self.rt.buffer("moe.z", T, W, dtype=torch.float32)
-        ops.gemm_simple(z, h, self.w_route)                     # float32 sums in k order, whatever the path
+        matmul_nt(self.rt, z, h, self.w_route)                  # float32 sums and output on both paths
         dense = self.rt.buffer("moe.dense", T, W, dtype=torch.float32)
         ops.moe_route(z, self.E, self.top, bool(self.sff), dense, ctx.tok_seq)
         gu = self.rt.buffer("moe.gu", T, 2 * self.F)
