@@ -60,6 +60,7 @@ _SIGNATURES = {
     },
     "retention": {
         "oe_retention_scan": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "oe_retention_chunks": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     },
     "moe": {
         "oe_moe_route": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _P],
@@ -434,11 +435,12 @@ def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache:
 
 def retention_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off_q: int, off_k: int, off_v: int,
                    cos: torch.Tensor | None, sin: torch.Tensor | None, rot_dims: int, k_scale: float,
-                   decay: torch.Tensor, ctx, heads: int, dk: int, dv: int) -> None:
+                   decay: torch.Tensor, ctx, heads: int, dk: int, dv: int, chunks: bool = False) -> None:
     """Per sequence and head, over the step's tokens in order: S <- decay_h S + k v^T; o = S^T q, with q and k
     turned by the token's position (first rot_dims dimensions, halves paired) and k times k_scale.  proj float32
     [T, >= ...] holds q at column off_q (H dk values), k at off_k (H dk), v at off_v (H dv); state float32
-    [slots, H, dk, dv] is read and written; o float32 [T, H dv]."""
+    [slots, H, dk, dv] is read and written; o float32 [T, H dv].  chunks: the kernel that takes a sequence's tokens
+    32 at a time (the same sums in another order: for prompts) instead of one by one."""
     _dev(o, state, proj, cos, sin, decay)
     for t, n in ((o, "o"), (state, "state"), (decay, "decay")):
         _f32c(t, n)
@@ -453,10 +455,11 @@ def retention_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off
         _f32c(sin, "sin")
         if rot_dims % 2 or rot_dims > dk or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
             raise KernelError("retention_scan: cos/sin must be [positions, rot_dims/2], rot_dims even and <= dk")
-    _check(_fn("retention", "oe_retention_scan")(
+    name = "retention_chunks" if chunks else "retention_scan"
+    _check(_fn("retention", "oe_" + name)(
         _ptr(o), _ptr(state), _ptr(proj), proj.stride(0), int(off_q), int(off_k), int(off_v), _ptr(cos), _ptr(sin),
         int(rot_dims), float(k_scale), _ptr(decay), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), _ptr(ctx.tok_pos), ctx.n_seqs,
-        heads, dk, dv, _stream()), "retention_scan")
+        heads, dk, dv, _stream()), name)
 
 
 # ---------------------------------------------------------------------------------------- moe.cu

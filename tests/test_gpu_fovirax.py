@@ -152,14 +152,16 @@ def test_routing_kernel_alone():
                 assert abs(dense[t, E].item() - torch.sigmoid(zc[t, E].double()).item()) < 1e-6
 
 
-def test_retention_kernel_alone_and_in_two_calls():
-    """S <- gamma S + k v^T, o = S^T q with the turn and the scaling of k, against the sums written out; a second
-    call goes on from the state the first one left; sizes that are no multiples of four."""
+@pytest.mark.parametrize("chunks", [False, True])
+def test_retention_kernel_alone_and_in_two_calls(chunks):
+    """S <- gamma S + k v^T, o = S^T q with the turn and the scaling of k, against the sums written out, token by
+    token and 32 tokens at a time; a second call goes on from the state the first one left (also from one form to
+    the other); sizes that are no multiples of four; a piece that is no multiple of a chunk."""
     from types import SimpleNamespace
     from oracle_engine_b200.csrc import ops
     torch.manual_seed(2)
     for H, dk, dv, rotd in [(2, 16, 24, 8), (3, 10, 5, 0), (1, 200, 40, 200), (2, 64, 33, 32)]:
-        T1, T2 = 21, 9
+        T1, T2 = (71, 40) if chunks else (21, 9)
         T = T1 + T2
         proj = torch.randn(T, 3 + 2 * H * dk + H * dv, dtype=torch.float64)
         off_q, off_k, off_v = 3, 3 + H * dk, 3 + 2 * H * dk
@@ -184,7 +186,7 @@ def test_retention_kernel_alone_and_in_two_calls():
         for lo, hi in ((0, T1), (T1, T)):
             ctx = SimpleNamespace(seq_slot=i32([1]), cu_q=i32([0, hi - lo]), tok_pos=i32(list(range(lo, hi))), n_seqs=1)
             ops.retention_scan(o[lo:hi], state, pc[lo:hi], off_q, off_k, off_v, cos, sin, rotd, dk ** -0.5,
-                               gamma.float().cuda(), ctx, H, dk, dv)
+                               gamma.float().cuda(), ctx, H, dk, dv, chunks=chunks and lo == 0)
         err = (o.double().cpu().reshape(T, H, dv) - want).abs().max().item()
         assert err < 2e-4 * want.abs().max().item(), (H, dk, dv, rotd, err)
         assert state[0].abs().max().item() == 0 and state[2].abs().max().item() == 0
@@ -319,7 +321,8 @@ def test_command_lines(models, tmp_path):
         _compare(helpers.collect(steps, files, requests), plain, requests, dtype, f"trace_run {dtype}")
     prompt = requests[0][:12]
     r = subprocess.run([sys.executable, str(helpers.ROOT / "bin" / "oracle"), "-m", folder, "--tokens",
-                        ",".join(map(str, prompt)), "-n", "6", "--temp", "0", "--dtype", "float32", "--ignore-eos"],
+                        ",".join(map(str, prompt)), "-n", "6", "--temp", "0", "--repeat-penalty", "1.0", "--dtype", "float32",
+                        "--ignore-eos"],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     assert [int(t) for t in r.stdout.split()] == pf.generate(plain, prompt, 6)
