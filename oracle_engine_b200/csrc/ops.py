@@ -60,7 +60,7 @@ _SIGNATURES = {
     },
     "retention": {
         "oe_retention_scan": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-        "oe_retention_chunks": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "oe_retention_chunks": [_P, _P, _P, _L, _I, _I, _I, _P, _P, _I, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P],
     },
     "moe": {
         "oe_moe_route": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _P],
@@ -435,12 +435,13 @@ def attn_split(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache:
 
 def retention_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off_q: int, off_k: int, off_v: int,
                    cos: torch.Tensor | None, sin: torch.Tensor | None, rot_dims: int, k_scale: float,
-                   decay: torch.Tensor, ctx, heads: int, dk: int, dv: int, chunks: bool = False) -> None:
+                   decay: torch.Tensor, ctx, heads: int, dk: int, dv: int, scratch: torch.Tensor | None = None) -> None:
     """Per sequence and head, over the step's tokens in order: S <- decay_h S + k v^T; o = S^T q, with q and k
     turned by the token's position (first rot_dims dimensions, halves paired) and k times k_scale.  proj float32
     [T, >= ...] holds q at column off_q (H dk values), k at off_k (H dk), v at off_v (H dv); state float32
-    [slots, H, dk, dv] is read and written; o float32 [T, H dv].  chunks: the kernel that takes a sequence's tokens
-    32 at a time (the same sums in another order: for prompts) instead of one by one."""
+    [slots, H, dk, dv] is read and written; o float32 [T, H dv].  scratch: float32 room for retention_scratch(...)
+    values; with it the chunked form runs (a sequence's tokens 32 at a time, the same sums in another order, for
+    prompts; it turns and scales q and k in place in proj), without it the tokens go one by one."""
     _dev(o, state, proj, cos, sin, decay)
     for t, n in ((o, "o"), (state, "state"), (decay, "decay")):
         _f32c(t, n)
@@ -455,11 +456,29 @@ def retention_scan(o: torch.Tensor, state: torch.Tensor, proj: torch.Tensor, off
         _f32c(sin, "sin")
         if rot_dims % 2 or rot_dims > dk or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
             raise KernelError("retention_scan: cos/sin must be [positions, rot_dims/2], rot_dims even and <= dk")
-    name = "retention_chunks" if chunks else "retention_scan"
-    _check(_fn("retention", "oe_" + name)(
+    if scratch is not None:
+        _f32c(scratch, "scratch")
+        max_chunks = scratch.numel() // (heads * dk * dv)
+        if max_chunks < T // RETENTION_CHUNK + ctx.n_seqs:
+            raise KernelError("retention_scan: the scratch is smaller than retention_scratch(...) values")
+        _check(_fn("retention", "oe_retention_chunks")(
+            _ptr(o), _ptr(state), _ptr(proj), proj.stride(0), int(off_q), int(off_k), int(off_v), _ptr(cos), _ptr(sin),
+            int(rot_dims), float(k_scale), _ptr(decay), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), _ptr(ctx.tok_seq),
+            _ptr(ctx.tok_pos), T, ctx.n_seqs, heads, dk, dv, _ptr(scratch), max_chunks, _stream()), "retention_chunks")
+        LAUNCHES[0] += 3
+        return
+    _check(_fn("retention", "oe_retention_scan")(
         _ptr(o), _ptr(state), _ptr(proj), proj.stride(0), int(off_q), int(off_k), int(off_v), _ptr(cos), _ptr(sin),
         int(rot_dims), float(k_scale), _ptr(decay), _ptr(ctx.seq_slot), _ptr(ctx.cu_q), _ptr(ctx.tok_pos), ctx.n_seqs,
-        heads, dk, dv, _stream()), name)
+        heads, dk, dv, _stream()), "retention_scan")
+
+
+RETENTION_CHUNK = 32      # tokens per chunk of the chunked retention; must equal CC of retention.cu
+
+
+def retention_scratch(n_tokens: int, n_seqs: int, heads: int, dk: int, dv: int) -> int:
+    """How many float32 values the chunked retention needs as scratch: a state per chunk and head."""
+    return (n_tokens // RETENTION_CHUNK + n_seqs) * heads * dk * dv
 
 
 # ---------------------------------------------------------------------------------------- moe.cu

@@ -7,10 +7,10 @@ layer whose memory is one matrix S [dk, dv] per head and sequence.
     S <- gamma_h S + k v^T;   o = S^T q                                     per head, S starts at zero
     x += Wo (concat_heads(o / sqrt(mean(o^2) + eps)) * gate)
 The projections leave their product as float32 on both paths, so nothing that enters the recurrence is rounded to
-16 bits; the turn, the scaling, S and the read-out are float32.  Two kernels (csrc/retention.cu): one takes a
-sequence's tokens one by one (decoding, and prompt steps of so many sequences that their chains fill the GPU), the
-other 32 at a time (the same sums chunk by chunk, no chain from token to token: prompt steps of few sequences).
-Both leave the same state up to rounding.
+16 bits; the turn, the scaling, S and the read-out are float32.  Two forms (csrc/retention.cu): a step in which
+some sequence brings CHUNK_FROM tokens or more cuts every sequence's tokens into chunks of 32 and computes all
+chunks side by side, only the state going from chunk to chunk (the same sums chunk by chunk); other steps, decoding
+among them, take the tokens one by one.  Both leave the same state up to rounding.
 """
 from __future__ import annotations
 
@@ -22,8 +22,7 @@ from .registry import MIXERS, Part
 from .spec import StateNeed, TensorDecl
 
 _NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
-CHUNK_FROM = 8          # a step whose longest sequence brings fewer tokens goes token by token
-CHAIN_BLOCKS = 296      # ... and so does one whose token-by-token blocks fill the GPU twice over
+CHUNK_FROM = 16         # a step whose longest sequence brings fewer tokens goes token by token
 
 
 @MIXERS.register("retention")
@@ -79,11 +78,6 @@ class Retention(Part):
     def first_weights(self):
         return self.w_in
 
-    def _in_chunks(self, ctx) -> bool:
-        """Measured on a B200 (16 heads of 64 x 128): one sequence of 2,048 tokens 1.98 ms token by token, 1.13 ms in
-        chunks; 8 sequences of 512 tokens 0.43 ms against 0.67 ms."""
-        return ctx.max_qlen >= CHUNK_FROM and ctx.n_seqs * self.H * ((self.dv + 31) // 32) < CHAIN_BLOCKS
-
     def forward(self, h, residual, ctx, cache, state, owns_cache=True, overwrite: bool = False):
         """overwrite: the output is written into `residual` (float32) instead of added."""
         T, f32 = h.shape[0], torch.float32
@@ -92,8 +86,12 @@ class Retention(Part):
         matmul_nt(self.rt, proj, h, self.w_in)
         cos, sin = self.position.tables() if self.rot else (None, None)
         o = self.rt.buffer("retention.o", T, vv, dtype=f32)
+        scratch = None
+        if ctx.max_qlen >= CHUNK_FROM:
+            scratch = self.rt.buffer("retention.chunks", ops.retention_scratch(T, ctx.n_seqs, self.H, self.dk, self.dv),
+                                     dtype=f32)
         ops.retention_scan(o, state["S"], proj, 0, qk, 2 * qk, cos, sin, self.rot, self.dk ** -0.5, self.decay, ctx,
-                           self.H, self.dk, self.dv, chunks=self._in_chunks(ctx))
+                           self.H, self.dk, self.dv, scratch=scratch)
         y = self.rt.buffer("retention.y", T, vv)
         ops.head_gate(y, o, proj[:, 2 * qk + vv:], None, self.H, self.dv, True, "silu", self.eps)
         matmul_nt(self.rt, residual, y, self.w_o, accumulate=not overwrite)

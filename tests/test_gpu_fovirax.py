@@ -184,9 +184,13 @@ def test_retention_kernel_alone_and_in_two_calls(chunks):
         pc = proj.float().cuda()
         i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")      # noqa: E731
         for lo, hi in ((0, T1), (T1, T)):
-            ctx = SimpleNamespace(seq_slot=i32([1]), cu_q=i32([0, hi - lo]), tok_pos=i32(list(range(lo, hi))), n_seqs=1)
+            ctx = SimpleNamespace(seq_slot=i32([1]), cu_q=i32([0, hi - lo]), tok_pos=i32(list(range(lo, hi))), n_seqs=1,
+                                  tok_seq=i32([0] * (hi - lo)))
+            scratch = None
+            if chunks and lo == 0:
+                scratch = torch.empty(ops.retention_scratch(hi - lo, 1, H, dk, dv), device="cuda")
             ops.retention_scan(o[lo:hi], state, pc[lo:hi], off_q, off_k, off_v, cos, sin, rotd, dk ** -0.5,
-                               gamma.float().cuda(), ctx, H, dk, dv, chunks=chunks and lo == 0)
+                               gamma.float().cuda(), ctx, H, dk, dv, scratch=scratch)
         err = (o.double().cpu().reshape(T, H, dv) - want).abs().max().item()
         assert err < 2e-4 * want.abs().max().item(), (H, dk, dv, rotd, err)
         assert state[0].abs().max().item() == 0 and state[2].abs().max().item() == 0
