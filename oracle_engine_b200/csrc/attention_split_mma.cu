@@ -11,6 +11,8 @@
 // then s <- cap tanh(s / cap) when cap > 0 (tanh as 1 - 2 / (exp(2x) + 1)); the softmax is online, in float32.
 // Mask: pos - window < key <= pos (window 0: every key up to pos).  Only the pages that hold a tile's visible
 // keys are read, so a windowed layer's cost does not grow with the context.
+// A step of single tokens may split a sequence's pages over `n_splits` CTAs (grid x): each writes its unnormalised
+// sums, maximum and denominator as float32, and attn_split_merge_kernel puts them together in split order.
 #include "common.cuh"
 
 #ifndef OE_DK
@@ -44,6 +46,8 @@ struct Args {
     int H, KVH, window;
     float scale, cap;
     int tokens_per_tile;
+    int n_splits;              // > 1: every sequence brings one token; grid x is the split
+    float* partial;            // [T, H, n_splits, DV + 2] when n_splits > 1
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -89,20 +93,26 @@ attn_split_mma_kernel(const Args a) {
     const int start = a.seq_start[b];
     const int G = a.H / a.KVH;
     const int tpt = a.tokens_per_tile;
-    const int t0 = blockIdx.x * tpt;
+    const int split = a.n_splits > 1 ? blockIdx.x : 0;
+    const int t0 = a.n_splits > 1 ? 0 : blockIdx.x * tpt;
     if (t0 >= qlen) return;
     const int nt = min(tpt, qlen - t0);
     const int pos_lo = start + t0, pos_hi = start + t0 + nt - 1;
     const int key_lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
-    const int j_lo = key_lo / BN, j_hi = pos_hi / BN;
+    int j_lo = key_lo / BN, j_hi = pos_hi / BN;
+    if (a.n_splits > 1) {
+        const int per = (j_hi - j_lo + a.n_splits) / a.n_splits;
+        j_lo += split * per;
+        j_hi = min(j_hi, j_lo + per - 1);
+    }
     const int* trow = a.tables + (size_t)b * a.max_pages;
-    const int n_blocks = j_hi - j_lo + 1;
+    const int n_blocks = max(0, j_hi - j_lo + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int row0 = warp * 16 + gid;
     const long long packed0 = a.cu_q[b] + t0;
 
-    load_page(smem, smem + K_TILE, a, trow[j_lo], kvh);
+    if (n_blocks > 0) load_page(smem, smem + K_TILE, a, trow[j_lo], kvh);
     cp_async_commit();
 
     int tok[2], pos[2], head[2];
@@ -247,6 +257,20 @@ attn_split_mma_kernel(const Args a) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
+    if (a.n_splits > 1) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (!valid[i]) continue;
+            float* p = a.partial + (((packed0 + tok[i]) * a.H + head[i]) * a.n_splits + split) * (long long)(DV + 2);
+#pragma unroll
+            for (int n = 0; n < DV / 8; n++) {
+                p[n * 8 + tig * 2] = oacc[n][2 * i];
+                p[n * 8 + tig * 2 + 1] = oacc[n][2 * i + 1];
+            }
+            if (tig == 0) { p[DV] = m_run[i]; p[DV + 1] = l_run[i]; }
+        }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 2; i++) {
         if (!valid[i]) continue;
@@ -255,6 +279,34 @@ attn_split_mma_kernel(const Args a) {
 #pragma unroll
         for (int n = 0; n < DV / 8; n++)
             *(uint32_t*)(o + n * 8) = pack_bf16(oacc[n][2 * i] * inv, oacc[n][2 * i + 1] * inv);
+    }
+}
+
+// One block per (token, head): the splits' sums put together in split order.  Maxima are in units of log2(e).
+__global__ void __launch_bounds__(128)
+attn_split_merge_kernel(bf16* out, const float* partial, int n_splits, const int* __restrict__ seq_qlen, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (seq_qlen[blockIdx.x / H] <= 0) {                 // a padding sequence: nothing was written for it
+        for (int d = threadIdx.x; d < DV; d += blockDim.x) out[(size_t)blockIdx.x * DV + d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const float* p = partial + (size_t)blockIdx.x * n_splits * (DV + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; s++) m = fmaxf(m, p[(size_t)s * (DV + 2) + DV]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ms = p[(size_t)s * (DV + 2) + DV];
+        if (ms != -INFINITY) l += exp2f(ms - m) * p[(size_t)s * (DV + 2) + DV + 1];
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; s++) {
+            const float ms = p[(size_t)s * (DV + 2) + DV];
+            if (ms != -INFINITY) acc = fmaf(exp2f(ms - m), p[(size_t)s * (DV + 2) + d], acc);
+        }
+        out[(size_t)blockIdx.x * DV + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -267,20 +319,30 @@ int oe_attn_split_mma_dims(int* dk, int* dv) { *dk = DK; *dv = DV; return 0; }
 // max_qlen: the most tokens any sequence of the step brings (sizes the grid).
 int oe_attn_split_mma(bf16* out, const bf16* q, long long q_stride, const bf16* kcache, const bf16* vcache,
                       const int* tables, int max_pages, const int* cu_q, const int* seq_start, const int* seq_qlen,
-                      int n_seqs, int max_qlen, int H, int KVH, int window, float scale, float cap, cudaStream_t st) {
+                      int n_seqs, int max_qlen, int H, int KVH, int window, float scale, float cap, int n_splits,
+                      float* partial, cudaStream_t st) {
     if (n_seqs <= 0 || max_qlen <= 0) return 0;
     if (KVH < 1 || H % KVH || H / KVH > NWARPS * 16 || n_seqs > 65535 || KVH > 65535) return OE_ERR_UNSUPPORTED;
+    if (n_splits > 1 && (max_qlen != 1 || partial == nullptr)) return OE_ERR_UNSUPPORTED;
     Args a;
     a.out = out; a.q = q; a.q_stride = q_stride; a.kcache = kcache; a.vcache = vcache; a.tables = tables;
     a.max_pages = max_pages; a.cu_q = cu_q; a.seq_start = seq_start; a.seq_qlen = seq_qlen;
     a.H = H; a.KVH = KVH; a.window = window; a.scale = scale; a.cap = cap;
     a.tokens_per_tile = (NWARPS * 16) / (H / KVH);
+    a.n_splits = n_splits > 1 ? n_splits : 1;
+    a.partial = partial;
     const size_t smem = (size_t)2 * (K_TILE + V_TILE);
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
+    }
+    if (a.n_splits > 1) {
+        // every sequence brings one token: row b of out is sequence b's (padding sequences leave theirs alone)
+        const int rc = oe_launch(attn_split_mma_kernel, dim3(a.n_splits, KVH, n_seqs), dim3(NWARPS * 32), smem, st, a);
+        if (rc) return rc;
+        return oe_launch(attn_split_merge_kernel, dim3(n_seqs * H), dim3(128), 0, st, out, (const float*)partial, a.n_splits, seq_qlen, H);
     }
     const dim3 grid((max_qlen + a.tokens_per_tile - 1) / a.tokens_per_tile, KVH, n_seqs);
     return oe_launch(attn_split_mma_kernel, grid, dim3(NWARPS * 32), smem, st, a);

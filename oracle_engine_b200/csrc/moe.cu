@@ -70,25 +70,43 @@ moe_route_kernel(const float* z, long long ldz, int E, int top, int has_gate, in
     if (has_gate && lane == 0) drow[E] = 1.f / (1.f + expf(-zr[E]));
 }
 
-template <typename T>
+// One thread takes 8 consecutive columns of one token (16 bytes of bfloat16) where an expert's columns come in
+// multiples of 8, else one column; the columns of an expert the token did not choose are written as zeros without
+// their gate and up values being read.
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 moe_dense_act_kernel(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t total = (size_t)n_tokens * F;
+    const int per_row = F / V;
+    const size_t total = (size_t)n_tokens * per_row;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = e / F;
-        const int c = (int)(e % F);
+        const size_t t = e / per_row;
+        const int c = (int)(e % per_row) * V;
         int grp = c / ff;
         if (grp > E) grp = E;
-        if (grp >= W) { a[e] = from_f32<T>(0.f); continue; }
-        const float w = dense[t * W + grp];
-        float r = 0.f;
+        const float w = grp < W ? dense[t * W + grp] : 0.f;
+        T out[V];
         if (w != 0.f) {
-            const float g = to_f32(gu[t * 2 * F + c]), u = to_f32(gu[t * 2 * F + F + c]);
-            r = g / (1.f + expf(-g)) * u * w;
+            T g[V], u[V];
+            if (V == 8) {
+                *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(gu + t * 2 * F + c);
+                *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(gu + t * 2 * F + F + c);
+            } else {
+                g[0] = gu[t * 2 * F + c];
+                u[0] = gu[t * 2 * F + F + c];
+            }
+#pragma unroll
+            for (int i = 0; i < V; i++) {
+                const float gf = to_f32(g[i]);
+                out[i] = from_f32<T>(gf / (1.f + expf(-gf)) * to_f32(u[i]) * w);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; i++) out[i] = from_f32<T>(0.f);
         }
-        a[e] = from_f32<T>(r);
+        if (V == 8) *reinterpret_cast<uint4*>(a + t * F + c) = *reinterpret_cast<uint4*>(out);
+        else a[t * F + c] = out[0];
     }
 }
 
@@ -96,10 +114,14 @@ template <typename T>
 int launch_act(T* a, const T* gu, const float* dense, int n_tokens, int F, int E, int ff, int W, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (F < 1 || ff < 1 || E < 0) return OE_ERR_UNSUPPORTED;
-    const size_t total = (size_t)n_tokens * F;
+    // 16-byte pieces: bfloat16, every expert's columns and the row a multiple of 8, aligned pointers
+    const bool vec = sizeof(T) == 2 && ff % 8 == 0 && F % 8 == 0 && !(((uintptr_t)a | (uintptr_t)gu) & 15);
+    const size_t total = (size_t)n_tokens * (vec ? F / 8 : F);
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    return oe_launch(moe_dense_act_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W);
+    if (vec)
+        return oe_launch(moe_dense_act_kernel<T, 8>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W);
+    return oe_launch(moe_dense_act_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, st, a, gu, dense, n_tokens, F, E, ff, W);
 }
 
 }  // namespace

@@ -584,7 +584,7 @@ def _attn_split_lib(dk: int, dv: int):
         lib = _build.load("attention_split_tc", defines={"OE_DK": dk, "OE_DV": dv})
         fn = lib.oe_attn_split_mma
         fn.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                       c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p]
+                       c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p]
         fn.restype = c_int
         _split_libs[(dk, dv)] = fn
     return fn
@@ -605,8 +605,19 @@ def attention_split(out, q, kcache, vcache, tables, ctx, n_heads: int, n_kv_head
     if tuple(kcache.shape[1:]) != (n_kv_heads, PAGE, dk) or tuple(vcache.shape[1:]) != (n_kv_heads, PAGE, dv) \
             or not (kcache.is_contiguous() and vcache.is_contiguous()):
         raise ops.KernelError("attention_split: the cache must be [pages, G, PAGE, dk] and [pages, G, PAGE, dv]")
+    # A step of single tokens: a sequence's pages are split over CTAs while the (sequence, KV head) pairs alone
+    # would leave SMs idle; the partial sums go through float32 scratch and a merge kernel.
+    n_splits, partial = 1, None
+    if ctx.all_decode and ctx.n_tokens == ctx.n_seqs:
+        keys = min(window, ctx.max_kvlen) if window else ctx.max_kvlen
+        n_splits = max(1, min(keys // PAGE + 1, (2 * _sm_count()) // max(1, ctx.n_seqs * n_kv_heads), 32))
+        if n_splits > 1:
+            partial = torch.empty(ctx.n_seqs * n_heads * n_splits * (dv + 2), dtype=torch.float32, device=out.device)
     code = _attn_split_lib(dk, dv)(out.data_ptr(), q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
                                    tables.data_ptr(), tables.shape[1], ctx.cu_q.data_ptr(), ctx.seq_start.data_ptr(),
                                    ctx.seq_qlen.data_ptr(), ctx.n_seqs, int(ctx.max_qlen), n_heads, n_kv_heads, int(window),
-                                   float(scale), float(cap or 0.0), ops._stream())
+                                   float(scale), float(cap or 0.0), n_splits,
+                                   None if partial is None else partial.data_ptr(), ops._stream())
     ops._check(code, "attention_split_mma")
+    if n_splits > 1:
+        ops.LAUNCHES[0] += 1
