@@ -10,7 +10,8 @@
 //                         when cap > 0, for the keys pos - window < j <= pos (all keys up to pos when window
 //                         is 0); online softmax in float32 over chunks of 32 keys at absolute multiples of 32,
 //                         so a token's result does not depend on how the step was cut or batched.  The
-//                         32-bit path's attention, and the first form of the bfloat16 path's.
+//                         32-bit path's attention, and the bfloat16 path's for head sizes that the tensor-core
+//                         kernel (attention_split_mma.cu) does not take.
 #include "common.cuh"
 
 namespace {
@@ -29,7 +30,8 @@ __global__ void __launch_bounds__(128)
 rope_split_kv_write_kernel(T* qkv, long long stride, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                            int rot, T* kcache, T* vcache, const int* __restrict__ tables, int max_pages,
                            const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, int H, int G, int dk,
-                           int dv, int has_kv) {
+                           int dv, int has_kv, int hpb) {
+    // grid y: block y turns the heads y hpb .. (y + 1) hpb - 1 (q heads, then k heads); the last y copies v
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -42,7 +44,9 @@ rope_split_kv_write_kernel(T* qkv, long long stride, const float* __restrict__ c
     const float* sr = sin_t + (size_t)pos * half;
     const int* trow = tables + (size_t)b * max_pages;
     const int n_rot_heads = H + (has_kv ? G : 0);
-    for (int e = threadIdx.x; e < n_rot_heads * dk; e += blockDim.x) {
+    const int e_lo = blockIdx.y * hpb * dk;
+    const int e_hi = min((int)(blockIdx.y + 1) * hpb, n_rot_heads) * dk;
+    for (int e = e_lo + threadIdx.x; e < e_hi; e += blockDim.x) {
         const int hh = e / dk, i = e % dk;
         if (i >= half && i < rot) continue;                     // written by its partner
         T* src = row + (size_t)hh * dk;
@@ -61,7 +65,7 @@ rope_split_kv_write_kernel(T* qkv, long long stride, const float* __restrict__ c
             dst[i] = src[i];
         }
     }
-    if (has_kv) {
+    if (has_kv && blockIdx.y == gridDim.y - 1) {
         const T* vsrc = row + (size_t)(H + G) * dk;
         for (int e = threadIdx.x; e < G * dv; e += blockDim.x) {
             const int g = e / dv, i = e % dv;
@@ -153,8 +157,13 @@ int launch_rope(T* qkv, long long stride, const float* cos_t, const float* sin_t
                 int dk, int dv, int has_kv, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (rot < 0 || rot % 2 || rot > dk || dk < 1 || dv < 1 || H < 1 || G < 1) return OE_ERR_UNSUPPORTED;
-    return oe_launch(rope_split_kv_write_kernel<T>, dim3(n_tokens), dim3(128), 0, st, qkv, stride, cos_t, sin_t, rot,
-                     kcache, vcache, tables, max_pages, tok_seq, tok_pos, H, G, dk, dv, has_kv);
+    // few tokens: a block per head, so that a token's loads are in flight together; many tokens: a block per token
+    const int n_rot_heads = H + (has_kv ? G : 0);
+    const int hpb = n_tokens <= 256 ? 1 : n_rot_heads;
+    const int by = (n_rot_heads + hpb - 1) / hpb + (has_kv ? 1 : 0);
+    if (by > 65535) return OE_ERR_UNSUPPORTED;
+    return oe_launch(rope_split_kv_write_kernel<T>, dim3(n_tokens, by), dim3(128), 0, st, qkv, stride, cos_t, sin_t, rot,
+                     kcache, vcache, tables, max_pages, tok_seq, tok_pos, H, G, dk, dv, has_kv, hpb);
 }
 
 template <typename T>

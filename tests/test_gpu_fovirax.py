@@ -196,6 +196,78 @@ def test_retention_kernel_alone_and_in_two_calls(chunks):
         assert state[0].abs().max().item() == 0 and state[2].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("dtype,dk,dv", [("float32", 20, 12), ("float32", 64, 32), ("bfloat16", 64, 32),
+                                         ("bfloat16", 32, 128), ("bfloat16", 24, 40)])
+def test_attention_kernels_alone_with_one_key_that_stands_out(dtype, dk, dv):
+    """Rotation, cache write and attention through the part's own dispatch on hand-made projections, with scattered
+    pages: the key just inside the window is made to dominate a query (the output is that key's value), then the key
+    just outside (the output must not know it), for queries in a prompt, in a second piece and decoded alone; and
+    the whole against the plain attention."""
+    from types import SimpleNamespace
+    from oracle_engine_b200.csrc.ops import PAGE
+    from oracle_engine_b200.engine.runtime import Runtime
+    from oracle_engine_b200.parts import attention_dispatch as ad
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    H, G, window, scale, cap, rotd = 4, 2, 70, 0.5, 30.0, 8
+    n, cuts = 200, [0, 150, 199, 200]                       # a prompt, a second piece, one decoded token
+    torch.manual_seed(5)
+    m = {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv, "scale": scale, "softcap": cap, "mask": {"size": window},
+         "rot": {"dims": rotd, "base": 100.0}}
+    rt = Runtime(tdt, torch.device("cuda"))
+    ang = torch.arange(n).double()[:, None] * pf.frequencies(m["rot"])[None, :]
+    cos, sin = torch.cos(ang).float().cuda(), torch.sin(ang).float().cuda()
+    pages = torch.tensor([5, 2, 7, 0], dtype=torch.int32)     # the sequence's pages, out of order, among 8
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32).cuda()      # noqa: E731
+    for inside in (True, False, None):
+        q = torch.randn(n, H, dk, dtype=torch.float64) * 0.3
+        k = torch.randn(n, G, dk, dtype=torch.float64) * 0.3
+        v = torch.randn(n, G, dv, dtype=torch.float64)
+        probes = [149, 180, 199]                             # one query in each of the three steps
+        if inside is not None:
+            for a, t in enumerate(probes):                    # a dimension of its own per probe, behind the turned ones
+                j = t - window + 1 if inside else t - window
+                q[t, :, rotd:] = 0
+                k[:, :, rotd + a] = 0
+                q[t, :, rotd + a] = 6.0
+                k[j, :, rotd + a] = 6.0                      # score 0.5 * 36 = 18 before the cap, every other key's about 0
+        qkv = torch.cat([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], 1).to(tdt)
+        ident = {"q": torch.eye(H * dk, dtype=torch.float64), "k": torch.eye(G * dk, dtype=torch.float64),
+                 "v": torch.eye(G * dv, dtype=torch.float64), "o": torch.eye(H * dv, dtype=torch.float64)}
+        hq = qkv.double()
+        want = torch.zeros(n, H * dv, dtype=torch.float64)
+        # the plain attention on the same (rounded) projections: each projection matrix picks its columns
+        wq = {"q": torch.eye(H * dk, hq.shape[1], dtype=torch.float64),
+              "k": torch.zeros(G * dk, hq.shape[1], dtype=torch.float64),
+              "v": torch.zeros(G * dv, hq.shape[1], dtype=torch.float64), "o": ident["o"]}
+        wq["k"][:, H * dk:H * dk + G * dk] = ident["k"]
+        wq["v"][:, H * dk + G * dk:] = ident["v"]
+        want = pf.window_attention(hq, wq, "", m)
+        kc = torch.zeros(8, G, PAGE, dk, dtype=tdt, device="cuda")
+        vc = torch.zeros(8, G, PAGE, dv, dtype=tdt, device="cuda")
+        tables = torch.full((1, 6), -1, dtype=torch.int32)
+        tables[0, :4] = pages
+        got = torch.zeros(n, H * dv, dtype=tdt, device="cuda")
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            T = hi - lo
+            ctx = SimpleNamespace(tok_seq=i32([0] * T), tok_pos=i32(list(range(lo, hi))), cu_q=i32([0, T]),
+                                  seq_start=i32([lo]), seq_qlen=i32([T]), n_seqs=1, n_tokens=T, max_qlen=T,
+                                  max_kvlen=hi, all_decode=T == 1)
+            part = qkv[lo:hi].cuda().contiguous()
+            out = torch.zeros(T, H * dv, dtype=tdt, device="cuda")
+            ad.split_mixer_core(rt, out, part, cos, sin, rotd, kc, vc, tables.cuda(), ctx, H, G, dk, dv, window, scale, cap)
+            got[lo:hi] = out
+        tol = 2e-5 if dtype == "float32" else 2e-2
+        err = (got.double().cpu() - want).abs().max().item()
+        assert err < tol * max(1.0, want.abs().max().item()), (dtype, dk, dv, inside, err)
+        if inside is not None:
+            for t in probes:
+                j = t - window + 1 if inside else t - window
+                for hh in range(H):
+                    o = got[t, hh * dv:(hh + 1) * dv].double().cpu()
+                    d = (o - v[j, hh // (H // G)]).abs().max().item()
+                    assert (d < 0.05) == inside, (dtype, dk, dv, inside, t, hh, d)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["V1", "V2", "V3"])
 def test_whole_decoded_pieces_and_batches_agree_with_plain(models, tmp_path, name, dtype):
