@@ -25,6 +25,10 @@ Mixer  (MIXERS; e.g. attention)
                  cache.kv [pages, 2, kv_heads, PAGE, head_dim]) and the page tables
         state    dict name -> tensor [slots, *shape] (index rows with ctx.seq_slot)
         owns_cache  False when the entry reads another entry's cache (write nothing)
+    optional: a mixer or feed-forward with `can_overwrite = True` also takes `overwrite=True` (its output is
+    written into `residual` instead of added), one with `can_scale = True` also takes `scale=(m, s)` (its output
+    times the constant m and the float32 per-channel vector s, or None, is added): arrangements that norm or
+    scale what a sublayer returns ask for these and fall back to a buffer of their own
 
 FeedForward  (FEED_FORWARDS; dense or routed)
     forward(h, residual, ctx)            adds its output into residual
@@ -37,6 +41,9 @@ PositionEncoding  (POSITIONS)            built once per model and name, shared b
 
 Block  (BLOCKS)                          the arrangement of mixer, feed-forward and norms
     forward(x, ctx, cache, state, owns_cache)   x float32 [T, hidden], updated in place
+    built as cls(mixer, feed_forward, mixer_norm, ffn_norm), or, when its LayerSpec gives `block_params`
+    (constants and tensor names of the arrangement itself), with params=, prefix= and runtime= as well;
+    parts() lists everything of it that declares or loads tensors
 """
 from __future__ import annotations
 
